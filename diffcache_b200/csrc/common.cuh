@@ -1,0 +1,168 @@
+// Shared device/host helpers for the diffcache_b200 kernels (sm_100a).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <cstdarg>
+#include <cstdio>
+
+#include "../../include/diffcache_b200.h"
+
+namespace dc {
+
+// ---- error reporting across the C ABI -------------------------------------------------------
+void set_error(const char* fmt, ...);
+int cuda_fail(cudaError_t err, const char* what);
+
+#define DC_CUDA_TRY(expr)                                  \
+    do {                                                   \
+        cudaError_t _e = (expr);                           \
+        if (_e != cudaSuccess) return dc::cuda_fail(_e, #expr); \
+    } while (0)
+
+#define DC_REQUIRE(cond, ...)            \
+    do {                                 \
+        if (!(cond)) {                   \
+            dc::set_error(__VA_ARGS__);  \
+            return DC_EINVAL;            \
+        }                                \
+    } while (0)
+
+inline cudaStream_t as_stream(uint64_t s) { return reinterpret_cast<cudaStream_t>(s); }
+
+int sm_count();  // SMs of the current device (cached per device)
+
+// ---- element-type helpers -------------------------------------------------------------------
+// Unpack eight 16-bit elements held in a uint4 into fp32.
+template <int DT>
+__device__ __forceinline__ void unpack8(const uint4& w, float (&f)[8]);
+
+template <>
+__device__ __forceinline__ void unpack8<DC_BF16>(const uint4& w, float (&f)[8]) {
+    // bf16 -> fp32 is a 16-bit shift: low element by shifting up, high element by masking.
+    f[0] = __uint_as_float(w.x << 16);
+    f[1] = __uint_as_float(w.x & 0xFFFF0000u);
+    f[2] = __uint_as_float(w.y << 16);
+    f[3] = __uint_as_float(w.y & 0xFFFF0000u);
+    f[4] = __uint_as_float(w.z << 16);
+    f[5] = __uint_as_float(w.z & 0xFFFF0000u);
+    f[6] = __uint_as_float(w.w << 16);
+    f[7] = __uint_as_float(w.w & 0xFFFF0000u);
+}
+
+template <>
+__device__ __forceinline__ void unpack8<DC_FP16>(const uint4& w, float (&f)[8]) {
+    float2 a = __half22float2(*reinterpret_cast<const __half2*>(&w.x));
+    float2 b = __half22float2(*reinterpret_cast<const __half2*>(&w.y));
+    float2 c = __half22float2(*reinterpret_cast<const __half2*>(&w.z));
+    float2 d = __half22float2(*reinterpret_cast<const __half2*>(&w.w));
+    f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y;
+    f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
+}
+
+template <int DT>
+__device__ __forceinline__ float elem_to_float(uint16_t h) {
+    if (DT == DC_BF16) return __uint_as_float(static_cast<uint32_t>(h) << 16);
+    return __half2float(__ushort_as_half(h));
+}
+
+template <int DT>
+__device__ __forceinline__ uint16_t float_to_elem(float f) {  // round to nearest even
+    if (DT == DC_BF16) return __bfloat16_as_ushort(__float2bfloat16_rn(f));
+    return __half_as_ushort(__float2half_rn(f));
+}
+
+// Streaming 16-byte load: the key/value stores are read once per step, so they should
+// not displace the (re-read) score and candidate buffers from L1/L2.
+__device__ __forceinline__ uint4 ld_stream16(const void* p) {
+    return __ldcs(reinterpret_cast<const uint4*>(p));
+}
+
+// Eight query elements [col0, col0+8) of the retrieval query of one problem as fp32.
+// q_mode 0: q already holds the group mean.  q_mode 1: q holds the `group` query heads of
+// the problem back to back; the mean is the fp32 sum in head order times 1/group, rounded
+// once to the element type (what torch's mean over a bf16 tensor produces).
+template <int DT>
+__device__ __forceinline__ void load_query8(const uint16_t* q, int64_t prob, int dim, int q_mode, int group,
+                                            int col0, float (&out)[8]) {
+    if (q_mode == 0) {
+        uint4 w = *reinterpret_cast<const uint4*>(q + prob * dim + col0);
+        unpack8<DT>(w, out);
+    } else {
+        float s[8];
+#pragma unroll
+        for (int j = 0; j < 8; j++) s[j] = 0.0f;
+        for (int g = 0; g < group; g++) {
+            uint4 w = *reinterpret_cast<const uint4*>(q + (prob * group + g) * dim + col0);
+            float f[8];
+            unpack8<DT>(w, f);
+#pragma unroll
+            for (int j = 0; j < 8; j++) s[j] += f[j];
+        }
+        float inv = 1.0f / static_cast<float>(group);
+#pragma unroll
+        for (int j = 0; j < 8; j++) out[j] = elem_to_float<DT>(float_to_elem<DT>(s[j] * inv));
+    }
+}
+
+
+// Transposing butterfly reduction.  Every lane holds NV partial values; the LPR lanes
+// that share a row (consecutive lanes, LPR a power of two) must be summed.  Instead of NV
+// full butterflies (NV*log2(LPR) shuffles) each exchange step halves the number of live
+// values per lane (lanes in the upper half of the exchange keep the upper half of the
+// values), so the cost is NV-1 shuffles while values remain, then plain butterfly steps.
+// Afterwards lane `l` holds treduce_count<NV,LPR>() fully reduced values v[0..count) whose
+// original indices start at treduce_base<NV,LPR>(l); lanes that differ only in the low
+// treduce_plain_bits<NV,LPR>() bits of their position hold identical copies.
+template <int NV, int LPR>
+__device__ __forceinline__ void treduce(float (&v)[NV], int lane) {
+    constexpr unsigned kFull = 0xFFFFFFFFu;
+    int nv = NV;
+#pragma unroll
+    for (int off = LPR / 2; off >= 1; off >>= 1) {
+        if (nv > 1) {
+            const int half = nv / 2;
+            const bool up = (lane & off) != 0;
+#pragma unroll
+            for (int j = 0; j < NV / 2; j++) {
+                if (j < half) {
+                    float send = up ? v[j] : v[j + half];
+                    float keep = up ? v[j + half] : v[j];
+                    v[j] = keep + __shfl_xor_sync(kFull, send, off);
+                }
+            }
+            nv = half;
+        } else {
+            v[0] += __shfl_xor_sync(kFull, v[0], off);
+        }
+    }
+}
+
+__host__ __device__ constexpr int ilog2(int x) { return x <= 1 ? 0 : 1 + ilog2(x / 2); }
+
+template <int NV, int LPR>
+__host__ __device__ constexpr int treduce_count() { return NV >= LPR ? NV / LPR : 1; }
+
+template <int NV, int LPR>
+__host__ __device__ constexpr int treduce_plain_bits() { return NV >= LPR ? 0 : ilog2(LPR) - ilog2(NV); }
+
+template <int NV, int LPR>
+__device__ __forceinline__ int treduce_base(int lane) {
+    int base = 0, half = NV / 2;
+#pragma unroll
+    for (int off = LPR / 2; off >= 1; off >>= 1) {
+        if (half >= 1) {
+            if (lane & off) base += half;
+            half /= 2;
+        }
+    }
+    return base;
+}
+
+// Ranking key of the reference: raw bits of fp32 (65536 - dot).
+__device__ __forceinline__ uint32_t dist_bits(float dot) { return __float_as_uint(65536.0f - dot); }
+
+}  // namespace dc

@@ -1,0 +1,277 @@
+"""Host-side mirror of the reference engine class ``DiffCacheCPU``.
+
+Same constructor, method names, argument meaning and error behaviour as the pyo3
+class in diffcache_cpu/src/lib.rs:523-660, with the work done by the CUDA engine
+behind the C ABI.  bf16 data crosses as ``uint16`` bit patterns exactly like the
+reference (src/diffcache/kvcache/diffcache.py:81-84); every array argument may be
+a numpy array (host) or a torch tensor (host or CUDA).
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional, Sequence
+
+import numpy as np
+
+from . import _lib
+
+BF16, FP16 = 0, 1
+
+_OPTION_DEFAULTS = dict(  # diffcache_cpu/src/lib.rs:556-566
+    max_ctx_len=1000000,
+    m=16,
+    ef_cons=200,
+    r_sq=None,
+    batch_search=False,
+    name="l0",
+    use_bruteforce=False,
+    attn_mass_threshold=0.9,
+    k_check_seq=[100, 200, 300, 400, 800, 1600, 3200, 6400, 12800, 25600],
+)
+
+
+def init_metrics() -> None:
+    """Counterpart of ``diffcache._cpu.init_metrics`` (lib.rs:662-665).
+
+    The reference installs a TCP exporter for its per-layer latency counters; this
+    engine keeps its counters in ``DiffCacheGPU.metrics`` instead, so there is
+    nothing to install."""
+    return None
+
+
+def _is_torch(x) -> bool:
+    return type(x).__module__.startswith("torch")
+
+
+def _ptr(x) -> Optional[int]:
+    if x is None:
+        return None
+    if isinstance(x, np.ndarray):
+        return x.ctypes.data
+    if _is_torch(x):
+        return x.data_ptr()
+    if isinstance(x, int):
+        return x
+    raise TypeError(f"unsupported buffer type {type(x)}")
+
+
+def _shape(x):
+    return tuple(x.shape)
+
+
+def _require_contiguous(x, what: str) -> None:
+    ok = x.flags["C_CONTIGUOUS"] if isinstance(x, np.ndarray) else x.is_contiguous()
+    if not ok:
+        # the reference reshapes with into_shape_with_order(...).unwrap(), lib.rs:384-385
+        raise ValueError(f"{what} must be C-contiguous")
+
+
+def _require_u16(x, what: str) -> None:
+    if isinstance(x, np.ndarray):
+        if x.dtype != np.uint16:
+            raise TypeError(f"{what}: expected uint16 bit patterns, got {x.dtype}")
+    elif x.element_size() != 2:
+        raise TypeError(f"{what}: expected a 16-bit element type, got {x.dtype}")
+
+
+def _current_stream(stream) -> int:
+    if stream is not None:
+        return int(stream)
+    import torch
+
+    return int(torch.cuda.current_stream().cuda_stream)
+
+
+class DiffCacheGPU:
+    """``DiffCacheCPU(bsz, q_head_num, kv_head_num, head_dim, **kwargs)`` on a B200.
+
+    Accepted kwargs are exactly the reference's (lib.rs:567-582): ``max_ctx_len, m,
+    ef_cons, r_sq, batch_search, name, use_bruteforce, attn_mass_threshold,
+    k_check_seq``; any other key raises (the reference panics with "Unknown option").
+    The graph parameters are accepted and ignored: this engine always runs the exact
+    scan, i.e. the reference's ``use_bruteforce=True`` semantics.  Two keyword-only
+    additions select the element type and device: ``dtype`` ("bf16" | "fp16") and
+    ``device`` (CUDA ordinal)."""
+
+    def __init__(self, bsz: int, q_head_num: int, kv_head_num: int, head_dim: int, **kwargs):
+        dtype = kwargs.pop("dtype", "bf16")
+        device = kwargs.pop("device", None)
+        opts = dict(_OPTION_DEFAULTS)
+        for key, value in kwargs.items():
+            if key not in opts:
+                raise ValueError(f"Unknown option {key}")
+            opts[key] = value
+        if opts["r_sq"] is None:
+            opts["r_sq"] = [4.0] * kv_head_num
+        self.options = opts
+        self.bsz, self.q_head_num, self.kv_head_num, self.head_dim = bsz, q_head_num, kv_head_num, head_dim
+        self.dtype = {"bf16": BF16, "fp16": FP16, BF16: BF16, FP16: FP16}[dtype]
+        if device is None:
+            import torch
+
+            device = torch.cuda.current_device()
+        self.device = int(device)
+        self.name = opts["name"]
+        self.metrics = {f"{self.name}_num_queries": 0}
+        self._lib = _lib.load()
+        handle = ctypes.c_void_p()
+        _lib.check(self._lib.dc_create(bsz, q_head_num, kv_head_num, head_dim, int(opts["max_ctx_len"]), self.dtype,
+                                       self.device, ctypes.byref(handle)))
+        self._h = handle
+
+    # -- lifetime ------------------------------------------------------------------------
+    def close(self) -> None:
+        h, self._h = getattr(self, "_h", None), None
+        if h:
+            self._lib.dc_destroy(h)
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    @property
+    def ctx_len(self) -> int:
+        out = ctypes.c_int64()
+        _lib.check(self._lib.dc_ctx_len(self._h, ctypes.byref(out)))
+        return out.value
+
+    @property
+    def group(self) -> int:
+        return self.q_head_num // self.kv_head_num
+
+    # -- reference API ---------------------------------------------------------------------
+    def prefill(self, keys, vals, neighbours=None, stream=None) -> None:
+        """lib.rs:601-611.  keys/vals ``(bsz, kv_head_num, seq_len, head_dim)`` uint16
+        (any strides whose last axis is contiguous); ``neighbours`` is accepted and
+        ignored (it only feeds the reference's NSW graph)."""
+        _require_u16(keys, "keys")
+        _require_u16(vals, "vals")
+        shp = _shape(keys)
+        if len(shp) != 4 or shp[0] != self.bsz or shp[1] != self.kv_head_num or shp[3] != self.head_dim:
+            raise ValueError(f"keys shape {shp} != (bsz, kv_head_num, seq_len, head_dim)")
+        if _shape(vals) != shp:
+            raise ValueError(f"vals shape {_shape(vals)} != keys shape {shp}")
+
+        def strides(x):
+            if isinstance(x, np.ndarray):
+                st = tuple(s // x.itemsize for s in x.strides)
+            else:
+                st = tuple(x.stride())
+            if st[3] != 1 and shp[3] > 1:
+                raise ValueError("head_dim axis must be contiguous")
+            return st
+
+        sk, sv = strides(keys), strides(vals)
+        if sk != sv:
+            raise ValueError("keys and vals must share one stride pattern")
+        _lib.check(self._lib.dc_prefill(self._h, _ptr(keys), _ptr(vals), shp[2], sk[0], sk[1], sk[2],
+                                        _current_stream(stream)))
+
+    def insert(self, keys, vals, stream=None) -> None:
+        """lib.rs:591-599.  keys/vals ``(bsz, kv_head_num, head_dim)``."""
+        for x, what in ((keys, "keys"), (vals, "vals")):
+            _require_u16(x, what)
+            _require_contiguous(x, what)
+            if _shape(x) != (self.bsz, self.kv_head_num, self.head_dim):
+                raise ValueError(f"{what} shape {_shape(x)} != (bsz, kv_head_num, head_dim)")
+        _lib.check(self._lib.dc_insert(self._h, _ptr(keys), _ptr(vals), _current_stream(stream)))
+
+    def query(self, out_keys, out_vals, queries, ef: int, out_idx=None, out_bits=None, stream=None) -> None:
+        """lib.rs:613-624 with ``use_bruteforce`` semantics (nsw.rs:592-630).
+
+        ``queries`` ``(bsz, kv_head_num, head_dim)``; ``out_keys/out_vals``
+        ``(bsz, kv_head_num, min(ef, ctx_len), head_dim)`` C-contiguous; row ``i`` is the
+        ``i``-th best key.  ``out_idx`` (int32) / ``out_bits`` (uint32) optionally receive the
+        selected row ids and their ranking keys."""
+        _require_u16(queries, "queries")
+        _require_contiguous(queries, "queries")
+        if _shape(queries) != (self.bsz, self.kv_head_num, self.head_dim):
+            raise ValueError(f"queries shape {_shape(queries)} != (bsz, kv_head_num, head_dim)")
+        ef_c = min(int(ef), self.ctx_len)
+        for x, what in ((out_keys, "out_keys"), (out_vals, "out_vals")):
+            if x is None:
+                continue
+            _require_u16(x, what)
+            _require_contiguous(x, what)
+            if _shape(x) != (self.bsz, self.kv_head_num, ef_c, self.head_dim):
+                raise ValueError(f"{what} shape {_shape(x)} != (bsz, kv_head_num, {ef_c}, head_dim)")
+        for x, what in ((out_idx, "out_idx"), (out_bits, "out_bits")):
+            if x is not None:
+                _require_contiguous(x, what)
+                if _shape(x) != (self.bsz, self.kv_head_num, ef_c):
+                    raise ValueError(f"{what} shape {_shape(x)} != (bsz, kv_head_num, {ef_c})")
+        _lib.check(self._lib.dc_query(self._h, _ptr(queries), int(ef), _ptr(out_keys), _ptr(out_vals), _ptr(out_idx),
+                                      _ptr(out_bits), _current_stream(stream)))
+        self.metrics[f"{self.name}_num_queries"] += 1
+
+    def query_streaming(self, cuda_stream: int, out_keys_gpu: int, out_vals_gpu: int, queries, ef: int) -> None:
+        """lib.rs:626-636: raw ``CUstream`` / device pointers as integers.  The reference
+        streams chunks as its graph search converges; an exact scan has a single final
+        answer, so this writes the complete result to the device buffers on ``cuda_stream``."""
+        _require_u16(queries, "queries")
+        _lib.check(self._lib.dc_query(self._h, _ptr(queries), int(ef), int(out_keys_gpu), int(out_vals_gpu), None, None,
+                                      int(cuda_stream)))
+
+    def get_keys(self) -> np.ndarray:
+        """lib.rs:646-649: stored keys as float32 ``(bsz, kv_head_num, ctx_len, head_dim)``."""
+        out = np.empty((self.bsz, self.kv_head_num, self.ctx_len, self.head_dim), np.float32)
+        _lib.check(self._lib.dc_get_keys(self._h, out.ctypes.data))
+        return out
+
+    def update_r_sq(self, r_sq: Sequence[float]) -> None:
+        """lib.rs:651-659: validated and otherwise unused (r_sq never enters QKDist)."""
+        arr = np.asarray(list(r_sq), np.float32)
+        _lib.check(self._lib.dc_update_r_sq(self._h, arr.ctypes.data, int(arr.shape[0])))
+        self.options["r_sq"] = [float(x) for x in arr]
+
+    def save(self, path: str) -> None:
+        """lib.rs:638-640.  Snapshot format: see :mod:`diffcache_b200.snapshot`."""
+        from . import snapshot
+
+        snapshot.save_engine(self, path)
+
+    def load(self, path: str, ctx_len: int) -> None:
+        """lib.rs:642-644."""
+        from . import snapshot
+
+        snapshot.load_engine(self, path, ctx_len)
+
+    # -- fused device path -----------------------------------------------------------------
+    def set_row_offset(self, row_offset: int) -> None:
+        _lib.check(self._lib.dc_set_row_offset(self._h, int(row_offset)))
+
+    def check_status(self, stream=None) -> None:
+        _lib.check(self._lib.dc_check_status(self._h, _current_stream(stream)))
+
+    def decode_attend(self, q, out, topk: int, res_k=None, res_v=None, res_len: int = 0, k_new=None, v_new=None,
+                      scale: float = 0.0, out_idx=None, out_lse=None, stream=None) -> None:
+        """One fused decode step on device tensors (see ``dc_decode_attend``).
+
+        ``q``/``out`` ``(bsz, q_head_num, head_dim)``; ``res_k/res_v`` a view
+        ``(bsz, kv_head_num, rows, head_dim)`` of the resident sink+window buffer whose first
+        ``res_len`` rows are valid; ``k_new/v_new`` ``(bsz, kv_head_num, head_dim)``."""
+        sb = sh = 0
+        if res_k is not None:
+            st = tuple(res_k.stride())
+            if st != tuple(res_v.stride()) or st[3] != 1 or st[2] != self.head_dim:
+                raise ValueError("res_k/res_v must share strides with contiguous rows of head_dim")
+            sb, sh = st[0], st[1]
+        _lib.check(self._lib.dc_decode_attend(self._h, _ptr(q), _ptr(k_new), _ptr(v_new), _ptr(res_k), _ptr(res_v), sb,
+                                              sh, int(res_len), int(topk), float(scale), _ptr(out), _ptr(out_idx),
+                                              _ptr(out_lse), _current_stream(stream)))
+
+    def local_topk(self, q, topk: int, out_bits, out_gidx, stream=None) -> None:
+        _lib.check(self._lib.dc_local_topk(self._h, _ptr(q), int(topk), _ptr(out_bits), _ptr(out_gidx),
+                                           _current_stream(stream)))
+
+    def attend_owned(self, q, sel_gidx, n_sel: int, out_acc, out_ml, res_k=None, res_v=None, res_len: int = 0,
+                     k_new=None, v_new=None, scale: float = 0.0, stream=None) -> None:
+        sb = sh = 0
+        if res_k is not None:
+            st = tuple(res_k.stride())
+            sb, sh = st[0], st[1]
+        _lib.check(self._lib.dc_attend_owned(self._h, _ptr(q), _ptr(sel_gidx), int(n_sel), _ptr(k_new), _ptr(v_new),
+                                             _ptr(res_k), _ptr(res_v), sb, sh, int(res_len), float(scale),
+                                             _ptr(out_acc), _ptr(out_ml), _current_stream(stream)))

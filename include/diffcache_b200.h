@@ -1,0 +1,297 @@
+/*
+ * diffcache_b200 — C ABI of the B200 (sm_100a) retrieval-attention engine.
+ *
+ * This is the boundary a maintainer of DiffCache binds instead of the Rust/pyo3
+ * module `diffcache._cpu` (diffcache_cpu/src/lib.rs:523-672).  Every entry point
+ * is plain C: opaque handle, raw pointers, sizes, and a CUDA stream passed as a
+ * 64-bit integer (the same convention the reference uses for `query_streaming`,
+ * diffcache_cpu/src/lib.rs:626-636).
+ *
+ * Conventions
+ *  - Every function returns 0 on success and a negative DC_E* code on failure;
+ *    nothing aborts, traps or throws across this boundary.  `dc_last_error()`
+ *    returns a thread-local, human readable description of the last failure.
+ *    (The reference reports the same conditions as Rust panics:
+ *    diffcache_cpu/src/lib.rs:332-333,353-354,376,579.)
+ *  - Element types cross the boundary as 16-bit patterns (bf16 or fp16), exactly
+ *    as the reference passes numpy uint16 views (diffcache_cpu/src/lib.rs:528-544).
+ *  - Unless stated otherwise a function only enqueues work on `stream` and
+ *    returns; device buffers must stay alive until that work completed.
+ *  - "problem" p = b * kv_heads + h is one (batch, kv-head) pair: one
+ *    `nsw::Index` of the reference (diffcache_cpu/src/lib.rs:296-313).
+ *  - Ranking key: dist = 65536.0f - dot(q, k) in fp32, compared by its raw bit
+ *    pattern, ties broken by the smaller row id
+ *    (diffcache_cpu/src/nsw.rs:74-91,129-139,600-615).
+ */
+#ifndef DIFFCACHE_B200_H
+#define DIFFCACHE_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define DC_OK 0
+#define DC_EINVAL (-1)   /* bad argument / shape (reference: assert!/panic!) */
+#define DC_ECUDA (-2)    /* a CUDA runtime call failed */
+#define DC_ENOMEM (-3)   /* device allocation failed */
+#define DC_ESTATE (-4)   /* call not valid in the engine's current state */
+#define DC_EDEVICE (-5)  /* a kernel reported an internal error status */
+
+#define DC_BF16 0
+#define DC_FP16 1
+
+/* Largest top-k / ef a select call accepts (reference: MAX_EF, diffcache_cpu/src/nsw.rs:14-20). */
+#define DC_MAX_TOPK 16384
+
+typedef struct dc_engine dc_engine;
+
+/* Description of the last failure on the calling thread ("" if none). */
+const char* dc_last_error(void);
+
+/* Library/ABI version (major*10000 + minor*100 + patch). */
+int dc_version(void);
+
+/* ------------------------------------------------------------------------- *
+ * Engine object: one per layer, as in src/diffcache/kvcache/diffcache.py:87-100
+ * ------------------------------------------------------------------------- */
+
+/*
+ * Replaces DiffCacheCPU.__new__ (diffcache_cpu/src/lib.rs:553-589) and
+ * DataLayer::new / Index::new (lib.rs:293-324, nsw.rs:680-698).
+ * Allocates the engine-owned HBM store K,V[bsz*kv_heads][max_ctx_len][head_dim]
+ * plus all per-step scratch, on CUDA device `device`.  head_dim must be 64, 128
+ * or 256; q_heads must be a multiple of kv_heads (lib.rs:294).
+ */
+int dc_create(int bsz, int q_heads, int kv_heads, int head_dim, int64_t max_ctx_len,
+              int dtype, int device, dc_engine** out);
+
+/* Frees everything dc_create allocated.  Synchronises the device first. */
+int dc_destroy(dc_engine* e);
+
+/*
+ * Sequence-sharded engines: the rows this engine holds are rows
+ * [row_offset, row_offset + ctx_len) of a longer logical sequence.  Row ids
+ * reported by dc_local_topk are local + row_offset.  Default 0.  No counterpart
+ * in the reference (it is single-process, src/diffcache/base.py:28).
+ */
+int dc_set_row_offset(dc_engine* e, int64_t row_offset);
+
+/*
+ * Replaces DiffCacheCPU.prefill (lib.rs:601-611) → DataLayer::prefill
+ * (lib.rs:329-347) → Index::prefill (nsw.rs:497-528): copies seq_len rows per
+ * problem into the store and sets ctx_len = seq_len.  `keys`/`vals` may be host
+ * or device memory; strides are in elements for the (batch, kv-head, row) axes,
+ * the head_dim axis must be contiguous.  The reference layout (B,Hkv,S,D)
+ * contiguous is stride_b = Hkv*S*D, stride_h = S*D, stride_s = D; the model's
+ * native (B,S,Hkv,D) layout is stride_b = S*Hkv*D, stride_h = D, stride_s = Hkv*D.
+ * The reference's `neighbours` argument only feeds the NSW graph and has no
+ * meaning for an exact scan, so it is not part of this ABI.
+ */
+int dc_prefill(dc_engine* e, const void* keys, const void* vals, int64_t seq_len,
+               int64_t stride_b, int64_t stride_h, int64_t stride_s, uint64_t stream);
+
+/*
+ * Replaces DiffCacheCPU.insert (lib.rs:591-599) → Index::insert (nsw.rs:544-557):
+ * appends one row per problem; keys/vals are (bsz, kv_heads, head_dim)
+ * contiguous, host or device.  Fails with DC_ESTATE when the store is full.
+ */
+int dc_insert(dc_engine* e, const void* keys, const void* vals, uint64_t stream);
+
+/* Number of valid rows per problem (DataLayer.ctx_len, lib.rs:191). */
+int dc_ctx_len(dc_engine* e, int64_t* out);
+
+/*
+ * Replaces DiffCacheCPU.query (lib.rs:613-624) with use_bruteforce semantics:
+ * DataLayer::query (lib.rs:373-404) → Index::search_bruteforce (nsw.rs:592-630).
+ * q_mean is (bsz, kv_heads, head_dim); ef is clamped to ctx_len; row i of
+ * out_keys/out_vals (bsz, kv_heads, ef, head_dim) is the i-th best row (smallest
+ * (dist bits, row id) first).  out_idx (int32) and out_bits (uint32), each
+ * (bsz, kv_heads, ef), are optional (NULL to skip).  All pointers may be host or
+ * device memory; when any of them is host memory the call synchronises `stream`
+ * before returning, as the reference call is synchronous.
+ */
+int dc_query(dc_engine* e, const void* q_mean, int ef, void* out_keys, void* out_vals,
+             int32_t* out_idx, uint32_t* out_bits, uint64_t stream);
+
+/*
+ * Synchronises `stream` and reports DC_EDEVICE if a kernel of an earlier
+ * asynchronous call on this engine flagged an internal inconsistency (the
+ * kernels never trap; they record a status word and produce padded output).
+ * The reference surfaces such conditions as Rust panics (e.g. nsw.rs:622).
+ */
+int dc_check_status(dc_engine* e, uint64_t stream);
+
+/*
+ * Replaces DiffCacheCPU.get_keys (lib.rs:646-649): fp32 copy of the stored keys,
+ * (bsz, kv_heads, ctx_len, head_dim), host or device destination; synchronous.
+ */
+int dc_get_keys(dc_engine* e, float* out);
+
+/*
+ * Raw copy of the stored rows, keys_out/vals_out (bsz, kv_heads, ctx_len,
+ * head_dim) 16-bit patterns, host or device; synchronous.  Feeds the snapshot
+ * that replaces DiffCacheCPU.save (lib.rs:638-640, nsw.rs:704-733); the way
+ * back is dc_prefill (DiffCacheCPU.load, lib.rs:642-644).
+ */
+int dc_export_rows(dc_engine* e, void* keys_out, void* vals_out);
+
+/*
+ * Replaces DiffCacheCPU.update_r_sq (lib.rs:651-659).  r_sq only enters the
+ * graph-construction metric (nsw.rs:141-146), never the query ranking
+ * (nsw.rs:129-139), so an exact scan only validates n == kv_heads.
+ */
+int dc_update_r_sq(dc_engine* e, const float* r_sq, int n);
+
+/*
+ * The fused decode step.  Replaces, for one layer, the chain
+ *   DiffCache.decode_pre_query_operation  (src/diffcache/kvcache/diffcache.py:191-194)
+ *   DiffCache.decode_query_kvcache        (diffcache.py:211-223)
+ *   DiffCache.decode_post_query_operation (diffcache.py:196-209)
+ *   flash_attn_with_kvcache(...)          (src/diffcache/base.py:134-142)
+ * without leaving HBM: group-mean query → score scan over the store → exact
+ * top-k → softmax attention of every query head over
+ * [top-k rows | resident rows | new token].
+ *
+ *  q        (bsz, q_heads, head_dim) device
+ *  k_new, v_new  (bsz, kv_heads, head_dim) device, or both NULL.  When given,
+ *           the new token takes part in attention as the last row and is also
+ *           appended to the resident buffers at row res_len (what flash-attn's
+ *           in-place append does), so res_k/res_v need room for res_len+1 rows.
+ *  res_k, res_v  resident (sink + local window) rows on the device,
+ *           element strides res_stride_b / res_stride_h, row stride head_dim;
+ *           in the reference layout this is kbuf[:, :, budget:, :]
+ *           (diffcache.py:48-66).  May be NULL when res_len == 0 and k_new == NULL.
+ *  topk     clamped to ctx_len; 0 skips retrieval.
+ *  scale    softmax scale; <= 0 selects head_dim^-0.5 (flash-attn default).
+ *  out      (bsz, q_heads, head_dim) device, engine dtype.
+ *  out_idx  optional (bsz, kv_heads, topk) int32 selected rows, best first.
+ *  out_lse  optional (bsz, q_heads) fp32 natural-log sum-exp of scaled scores.
+ */
+int dc_decode_attend(dc_engine* e, const void* q, const void* k_new, const void* v_new,
+                     void* res_k, void* res_v, int64_t res_stride_b, int64_t res_stride_h,
+                     int res_len, int topk, float scale, void* out, int32_t* out_idx,
+                     float* out_lse, uint64_t stream);
+
+/* ------------------------------------------------------------------------- *
+ * Sequence-sharded decode (one engine per GPU holds a contiguous row range).
+ * No counterpart in the reference (single GPU); the semantics are those of the
+ * single-engine path applied to the concatenated rows.
+ * ------------------------------------------------------------------------- */
+
+/*
+ * Local half of a sharded step: group-mean query, scan of this engine's rows,
+ * local top-k.  out_bits/out_gidx are (bsz*kv_heads, topk) uint32, best first;
+ * out_gidx = local row + row_offset.  When ctx_len < topk the tail is padded
+ * with bits = 0xFFFFFFFF, gidx = 0xFFFFFFFF (never selected by a merge).
+ */
+int dc_local_topk(dc_engine* e, const void* q, int topk, uint32_t* out_bits,
+                  uint32_t* out_gidx, uint64_t stream);
+
+/*
+ * Second half: attention of every query head over the rows of `sel_gidx`
+ * ((bsz*kv_heads, n_sel) uint32, global ids) that this engine owns, plus the
+ * resident rows / new token given (pass res_len = 0 and NULLs on ranks that hold
+ * neither sink nor window).  Writes un-normalised partial results:
+ *   out_acc (bsz, q_heads, head_dim) fp32 = sum_j exp(s_j - m) v_j
+ *   out_ml  (bsz, q_heads, 2) fp32 = (m in log2 units, l = sum_j exp2(s_j - m))
+ * which dc_lse_combine merges.
+ */
+int dc_attend_owned(dc_engine* e, const void* q, const uint32_t* sel_gidx, int n_sel,
+                    const void* k_new, const void* v_new, void* res_k, void* res_v,
+                    int64_t res_stride_b, int64_t res_stride_h, int res_len, float scale,
+                    float* out_acc, float* out_ml, uint64_t stream);
+
+/* ------------------------------------------------------------------------- *
+ * Stateless kernels (device pointers only).  The engine calls are compositions
+ * of these; they are exported for sharded drivers and for parity tests.
+ * ------------------------------------------------------------------------- */
+
+/*
+ * Score scan = the loop body of Index::search_bruteforce (nsw.rs:601-607) with
+ * Index::distance QKDist (nsw.rs:129-139).  keys: n_prob problems of n rows,
+ * problem stride `prob_stride` elements, row stride head_dim.  q_mode 0: q is
+ * (n_prob, head_dim) already group-averaged; q_mode 1: q is (n_prob*group,
+ * head_dim) query heads and the group mean (fp32 sum in head order, times
+ * 1/group, rounded to the element type — torch's `.mean(dim=2)` of
+ * diffcache.py:193) is formed in the kernel prologue.  Writes
+ * scores[p*score_stride + i] = bits(65536.0f - dot) and, if minmax != NULL,
+ * atomically folds (min, max) of those bits into minmax[2p], minmax[2p+1]
+ * (caller initialises to 0xFFFFFFFF, 0).
+ */
+int dc_score_scan(const void* keys, int64_t prob_stride, int n_prob, int64_t n, int head_dim,
+                  int dtype, const void* q, int q_mode, int group, uint32_t* scores,
+                  int64_t score_stride, uint32_t* minmax, uint64_t stream);
+
+/*
+ * Exact top-k select = the BinaryHeap<u64> of search_bruteforce
+ * (nsw.rs:600-615,621): the k smallest 64-bit keys (bits << 32 | id), ascending.
+ * bits: (n_prob, n) with row stride in_stride.  ids == NULL means id = position.
+ * minmax (2 per problem) may be NULL (computed in the kernel).  out_bits /
+ * out_ids: (n_prob, k) with row stride out_stride; either may be NULL.  When
+ * k > n the tail beyond n is padded with 0xFFFFFFFF (bits and ids).  `scratch` must hold dc_select_scratch_bytes(n_prob) zeroed bytes (a status
+ * word: a non-zero value after the call reports an internal inconsistency).
+ */
+int dc_topk_select(const uint32_t* bits, const uint32_t* ids, int64_t in_stride, int n_prob,
+                   int64_t n, int k, const uint32_t* minmax, uint32_t* out_bits,
+                   uint32_t* out_ids, int64_t out_stride, void* scratch, uint64_t stream);
+int64_t dc_select_scratch_bytes(int n_prob);
+
+/*
+ * Sparse gather-attention + split-K merge = flash_attn_with_kvcache over the
+ * gathered buffer (base.py:134-142), reading rows in place.  Store pointers as in
+ * dc_score_scan; sel (n_prob, sel_stride) uint32 row ids minus `sel_base`; only
+ * ids with sel_base <= id < sel_base + n_rows are attended (others are skipped).
+ * Exactly one of (out, out_acc/out_ml) must be given: `out` is the normalised
+ * result in the element type, out_acc/out_ml the un-normalised partials.
+ * `scratch` must hold dc_attend_scratch_bytes(n_prob, group, head_dim) bytes.
+ */
+int dc_sparse_attend(const void* k_store, const void* v_store, int64_t prob_stride, int64_t n_rows,
+                     int n_prob, int kv_heads, int group, int head_dim, int dtype, const void* q,
+                     const uint32_t* sel, int64_t sel_stride, int n_sel, int64_t sel_base,
+                     const void* k_new, const void* v_new, void* res_k, void* res_v,
+                     int64_t res_stride_b, int64_t res_stride_h, int res_len, float scale,
+                     void* out, float* out_lse, float* out_acc, float* out_ml, void* scratch,
+                     uint64_t stream);
+int64_t dc_attend_scratch_bytes(int n_prob, int group, int head_dim);
+
+/*
+ * Log-sum-exp merge of `n_part` partial results laid out as
+ * acc (n_part, rows, head_dim) fp32 and ml (n_part, rows, 2) fp32 into
+ * out (rows, head_dim) in the element type and optional lse (rows) fp32.
+ */
+int dc_lse_combine(const float* acc, const float* ml, int n_part, int64_t rows, int head_dim,
+                   int dtype, void* out, float* out_lse, uint64_t stream);
+
+/* Gather rows: out[p][i][:] = store[p][ids[p][i]][:]  (nsw.rs:623-629). */
+int dc_gather_rows(const void* store, int64_t prob_stride, int n_prob, int head_dim,
+                   const uint32_t* ids, int64_t ids_stride, int n_ids, void* out, uint64_t stream);
+
+/* ------------------------------------------------------------------------- *
+ * Product-quantisation baseline (asymmetric distance + exact rerank).
+ * No counterpart in the reference: evaluation/impl/pqcache is an empty
+ * directory.  Definition: M subspaces of head_dim/M dims, 256 centroids each;
+ * lut[m][c] = <q_m, centroid[m][c]> (fp32, dims in order), score =
+ * sum_m lut[m][code[m]] in increasing m, ranking key = bits(65536.0f - score).
+ * ------------------------------------------------------------------------- */
+
+/* lut (n_prob, M, 256) fp32 from q (n_prob, head_dim, element type; q_mode as in
+ * dc_score_scan) and centroids (n_prob, M, 256, head_dim/M) fp32. */
+int dc_pq_build_lut(const void* q, int q_mode, int group, int dtype, const float* centroids,
+                    int n_prob, int head_dim, int n_sub, float* lut, uint64_t stream);
+
+/* ADC scan over codes (n_prob, n, M) uint8 → scores/minmax as dc_score_scan. */
+int dc_pq_adc_scan(const uint8_t* codes, int64_t prob_stride, int n_prob, int64_t n, int n_sub,
+                   const float* lut, uint32_t* scores, int64_t score_stride, uint32_t* minmax,
+                   uint64_t stream);
+
+/* Exact re-scoring of candidate rows: out_bits[p][i] = bits(65536 - <q_p, K[p][ids[p][i]]>). */
+int dc_rerank_scores(const void* keys, int64_t prob_stride, int n_prob, int head_dim, int dtype,
+                     const void* q, int q_mode, int group, const uint32_t* ids, int64_t ids_stride,
+                     int n_ids, uint32_t* out_bits, uint64_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DIFFCACHE_B200_H */

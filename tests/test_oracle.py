@@ -1,0 +1,132 @@
+"""CPU tests: the oracle against the golden vectors and against independent restatements."""
+import numpy as np
+import pytest
+import torch
+
+from tests import util
+
+
+def test_select_kat_heap_and_sort(oracle_lib):
+    for case in util.load_select_kat():
+        vals = np.asarray(case["values"], np.int64)
+        # order-preserving map into positive-float bit patterns (the reference compares dist as
+        # f32 and as raw bits, which agree only for dist >= 0: nsw.rs:127,136-137)
+        bits = (vals + util.KAT_OFFSET).astype(np.uint32)
+        for method in ("heap", "sort"):
+            ob, oi = oracle_lib.topk(bits, case["cap"], method=method)
+            got = (ob.astype(np.int64) - util.KAT_OFFSET).tolist()
+            assert got == case["expected"], case["name"]
+            # ties go to the smaller position, keys strictly ascending
+            keys = (ob.astype(np.uint64) << np.uint64(32)) | oi.astype(np.uint64)
+            assert np.all(keys[1:] > keys[:-1])
+            assert np.array_equal(bits[oi], ob)
+
+
+def test_heap_equals_sort_on_tie_heavy_streams(oracle_lib):
+    rng = np.random.default_rng(1)
+    for trial in range(200):
+        n = int(rng.integers(1, 400))
+        ef = int(rng.integers(1, 64))
+        # quantised positive floats: many exact ties, like fp32(65536 - dot)
+        d = (65536.0 - np.round(rng.normal(0, 3, n) * 4) / 4).astype(np.float32)
+        bits = d.view(np.uint32)
+        hb, hi = oracle_lib.topk(bits, ef, method="heap")
+        sb, si = oracle_lib.topk(bits, ef, method="sort")
+        assert np.array_equal(hb, sb) and np.array_equal(hi, si)
+
+
+def test_conversions_match_torch_and_numpy(oracle_lib):
+    rng = np.random.default_rng(2)
+    x = (rng.standard_normal(200000) * np.exp(rng.standard_normal(200000) * 4)).astype(np.float32)
+    x[:8] = [0.0, -0.0, 65504.0, 65519.9, 65520.0, 1e-8, 6e-8, -3e-5]
+    want_bf = torch.from_numpy(x).to(torch.bfloat16).view(torch.uint16).numpy()
+    assert np.array_equal(oracle_lib.from_f32(x, 0), want_bf)
+    with np.errstate(over="ignore"):
+        want_h = x.astype(np.float16).view(np.uint16)
+    assert np.array_equal(oracle_lib.from_f32(x, 1), want_h)
+    allh = np.arange(65536, dtype=np.uint16)
+    ref = allh.view(np.float16).astype(np.float32)
+    got = oracle_lib.to_f32(allh, 1)
+    ok = ~np.isnan(ref)
+    assert np.array_equal(got.view(np.uint32)[ok], ref.view(np.uint32)[ok])
+    assert np.array_equal(oracle_lib.to_f32(allh, 0).view(np.uint32), allh.astype(np.uint32) << 16)
+
+
+@pytest.mark.parametrize("dtype", ["bf16", "fp16"])
+def test_group_mean_matches_torch_mean(oracle_lib, dtype):
+    """The reference forms the retrieval query with torch's CUDA mean over a 16-bit tensor
+    (src/diffcache/kvcache/diffcache.py:193): fp32 sum, times 1/G, one rounding.  (torch's CPU
+    kernel rounds the sum to 16 bits before dividing, so it is only compared where that is exact;
+    the CUDA kernel is compared on a device in tests/test_gpu_parity.py.)"""
+    td = {"bf16": torch.bfloat16, "fp16": torch.float16}[dtype]
+    g = torch.Generator().manual_seed(3)
+    for group in (1, 2, 4, 7, 8):
+        q = (torch.randn(6, 4, group, 128, generator=g) * 3).to(td)
+        got = oracle_lib.group_mean(util.u16(q.reshape(-1, 128)), group, util.dtype_code(dtype))
+        acc = torch.zeros(6, 4, 128)
+        for j in range(group):
+            acc = acc + q[:, :, j].float()
+        want = (acc * torch.tensor(1.0 / group, dtype=torch.float32)).to(td)
+        assert np.array_equal(got, util.u16(want.reshape(-1, 128)))
+        if group == 1:
+            assert np.array_equal(got, util.u16(q.mean(dim=2).reshape(-1, 128)))
+
+
+def test_scores_match_float64_definition(oracle_lib):
+    g = torch.Generator().manual_seed(4)
+    k = (torch.randn(3000, 128, generator=g) * 2).to(torch.bfloat16)
+    q = (torch.randn(128, generator=g) * 2).to(torch.bfloat16)
+    bits = oracle_lib.score_rows(util.u16(k), util.u16(q), 0)
+    dot = (k.double() @ q.double()).numpy()
+    want = (np.float32(65536.0) - dot.astype(np.float32)).astype(np.float32)
+    assert np.array_equal(bits, want.view(np.uint32))
+    fast = oracle_lib.score_rows(util.u16(k), util.u16(q), 0, exact=False)
+    # fp32 accumulation may move a value by at most one dist ulp
+    assert np.max(np.abs(fast.view(np.float32).astype(np.float64) - want.astype(np.float64))) <= 2 ** -7
+
+
+def test_query_orders_and_gathers(oracle_lib):
+    k, v, q = util.small_problem(2, 2, 4, 5000, 128, seed=5)
+    P = 4
+    ku, vu = util.u16(k).reshape(P, 5000, 128), util.u16(v).reshape(P, 5000, 128)
+    qm = oracle_lib.group_mean(util.u16(q).reshape(-1, 128), 4, 0)
+    res = oracle_lib.query(ku, vu, qm, 300, 0)
+    for p in range(P):
+        bits = oracle_lib.score_rows(ku[p], qm[p], 0)
+        sb, si = oracle_lib.topk(bits, 300, method="sort")
+        assert np.array_equal(res["idx"][p], si) and np.array_equal(res["bits"][p], sb)
+        assert np.array_equal(res["keys"][p], ku[p][si]) and np.array_equal(res["vals"][p], vu[p][si])
+    # ef larger than the store is clamped (lib.rs:374)
+    res2 = oracle_lib.query(ku[:, :50].copy(), vu[:, :50].copy(), qm, 300, 0)
+    assert res2["ef"] == 50 and res2["idx"].shape == (P, 50)
+
+
+def test_attention_matches_torch_float64(oracle_lib):
+    g = torch.Generator().manual_seed(6)
+    P, G, n, D = 3, 4, 257, 128
+    k = torch.randn(P, n, D, generator=g).to(torch.bfloat16)
+    v = torch.randn(P, n, D, generator=g).to(torch.bfloat16)
+    q = torch.randn(P * G, D, generator=g).to(torch.bfloat16)
+    scale = D ** -0.5
+    of, oe, lse = oracle_lib.attend(util.u16(k), util.u16(v), util.u16(q), G, scale, 0)
+    s = torch.einsum("pgd,pnd->pgn", q.view(P, G, D).double(), k.double()) * scale
+    want = torch.einsum("pgn,pnd->pgd", torch.softmax(s, -1), v.double()).reshape(P * G, D)
+    assert np.allclose(of, want.float().numpy(), rtol=1e-6, atol=1e-7)
+    assert np.array_equal(oe, util.u16(want.float().to(torch.bfloat16)))
+    assert np.allclose(lse, torch.logsumexp(s, -1).reshape(-1).float().numpy(), rtol=1e-6)
+
+
+def test_pq_definitions(oracle_lib):
+    rng = np.random.default_rng(7)
+    P, D, M, n = 2, 128, 16, 1000
+    cen = rng.standard_normal((P, M, 256, D // M)).astype(np.float32)
+    q = torch.randn(P, D).to(torch.bfloat16)
+    lut = oracle_lib.pq_build_lut(util.u16(q), cen, M, 0)
+    want = np.einsum("pmd,pmcd->pmc", q.float().numpy().reshape(P, M, D // M).astype(np.float64), cen.astype(np.float64))
+    assert np.allclose(lut, want, rtol=1e-5, atol=1e-5)
+    codes = rng.integers(0, 256, (n, M), dtype=np.uint8)
+    bits = oracle_lib.pq_adc_scores(codes, lut[0])
+    s = np.zeros(n, np.float32)
+    for m in range(M):
+        s = (s + lut[0, m, codes[:, m]]).astype(np.float32)
+    assert np.array_equal(bits, (np.float32(65536.0) - s).astype(np.float32).view(np.uint32))

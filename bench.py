@@ -1,0 +1,366 @@
+#!/usr/bin/env python
+"""Benchmark of the decode-time retrieval-attention step.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One "step" is one fused decode step of one layer over one batch: group-mean query -> score
+scan over every cached key -> exact top-k -> softmax attention over top-k + sink + window
+(+ the new token).  The workload at every N is configuration 1 of the baseline (batch 16,
+32 query / 8 KV heads, head_dim 128, 131072-token context, bf16, top-k 2048 + 64 sink + 512
+window) on synthetic seeded inputs; with N > 1 every rank runs its own batch (the
+(batch, kv-head) problems are independent, so there is no data-path collective) and the
+reported value is the aggregate over ranks: weak scaling.
+
+Prints ONE JSON line (rank 0).  `--impl reference` times the CPU restatement of the
+reference engine's exact-scan path (the Rust crate cannot be built here) on the host cores.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import numpy as np  # noqa: E402
+import torch  # noqa: E402
+
+from diffcache_b200 import synth  # noqa: E402
+
+METRIC = "decode attention steps/sec at 128K ctx"
+UNIT = "steps/s"
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.gpu_index)], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, reasons, smax = [], set(), None
+        try:
+            for line in open(self.path):
+                parts = [p.strip() for p in line.split(",")]
+                if len(parts) < 9:
+                    continue
+                try:
+                    sm.append(float(parts[1]))
+                    smax = float(parts[2])
+                except ValueError:
+                    continue
+                for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"),
+                                     parts[5:9]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+            os.unlink(self.path)
+        except Exception:
+            pass
+        if sm:
+            out.update(sm_mhz=float(np.median(sm)), sm_max_mhz=smax, reasons=sorted(reasons), samples=len(sm))
+        return out
+
+
+def dist_setup(n_gpus: int):
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        import torch.distributed as dist
+
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    else:
+        torch.cuda.set_device(0)
+    return world, rank, local
+
+
+def build_step_inputs(cfg: synth.StepConfig, seed: int, device):
+    """Engine + resident buffers + per-step inputs for one rank, all resident in HBM."""
+    from diffcache_b200 import DiffCacheGPU
+
+    dt = synth.torch_dtype(cfg.dtype)
+    n_r = cfg.n_retrieval
+    eng = DiffCacheGPU(cfg.batch, cfg.q_heads, cfg.kv_heads, cfg.head_dim, max_ctx_len=n_r, dtype=cfg.dtype,
+                       device=device.index, use_bruteforce=True)
+    # sequence = [sink | retrieval region | window]; the newest window token is the step's new token
+    k, v = synth.make_kv(cfg.batch, cfg.kv_heads, cfg.context, cfg.head_dim, seed, cfg.dtype, device=device)
+    q = synth.make_query(k[:, :, cfg.sink:cfg.sink + n_r], cfg.group, seed).contiguous()
+    eng.prefill(k[:, :, cfg.sink:cfg.sink + n_r], v[:, :, cfg.sink:cfg.sink + n_r])
+    res_rows = cfg.sink + cfg.window - 1
+    res_k = torch.zeros((cfg.batch, cfg.kv_heads, cfg.sink + cfg.window + 8, cfg.head_dim), dtype=dt, device=device)
+    res_v = torch.zeros_like(res_k)
+    for dst, src in ((res_k, k), (res_v, v)):
+        dst[:, :, :cfg.sink] = src[:, :, :cfg.sink]
+        dst[:, :, cfg.sink:res_rows] = src[:, :, cfg.sink + n_r:cfg.context - 1]
+    k_new = k[:, :, -1].contiguous()
+    v_new = v[:, :, -1].contiguous()
+    torch.cuda.synchronize()
+    host = dict(k=k, v=v)  # kept only until the caller drops it (CPU baseline sample)
+    return eng, q, res_k, res_v, res_rows, k_new, v_new, host
+
+
+def cpu_reference_step_rate(cfg: synth.StepConfig, k_dev, v_dev, q_dev, budget_s: float, max_steps: int,
+                            sample_batch: int):
+    """Times the CPU restatement of DataLayer::query (brute force) + attention on a sample of the
+    batch and scales to whole-batch steps/s."""
+    import oracle
+
+    oracle.build()
+    code = 0 if cfg.dtype == "bf16" else 1
+    sb = min(sample_batch, cfg.batch)
+    n_r, D, G = cfg.n_retrieval, cfg.head_dim, cfg.group
+    P = sb * cfg.kv_heads
+
+    def u16(t):
+        return t.detach().cpu().contiguous().view(torch.uint16).numpy()
+
+    ks = u16(k_dev[:sb, :, cfg.sink:cfg.sink + n_r]).reshape(P, n_r, D)
+    vs = u16(v_dev[:sb, :, cfg.sink:cfg.sink + n_r]).reshape(P, n_r, D)
+    res_k = np.concatenate([u16(k_dev[:sb, :, :cfg.sink]), u16(k_dev[:sb, :, cfg.sink + n_r:])], axis=2).reshape(P, -1, D)
+    res_v = np.concatenate([u16(v_dev[:sb, :, :cfg.sink]), u16(v_dev[:sb, :, cfg.sink + n_r:])], axis=2).reshape(P, -1, D)
+    qh = u16(q_dev[:sb]).reshape(P * G, D)
+    threads = oracle.max_threads()
+    times = []
+    t_end = time.time() + budget_s
+    for _ in range(max_steps):
+        t0 = time.perf_counter()
+        qm = oracle.group_mean(qh, G, code)
+        res = oracle.query(ks, vs, qm, cfg.topk, code, exact=False, n_threads=threads)
+        kk = np.ascontiguousarray(np.concatenate([res["keys"], res_k], axis=1))
+        vv = np.ascontiguousarray(np.concatenate([res["vals"], res_v], axis=1))
+        oracle.attend(kk, vv, qh, G, D ** -0.5, code, n_threads=threads)
+        times.append(time.perf_counter() - t0)
+        if time.time() > t_end and len(times) >= 2:
+            break
+    per_sample = float(np.median(times))
+    per_step = per_sample * (cfg.batch / sb)
+    return dict(value=1.0 / per_step, unit=UNIT, cores=threads, kind="port",
+                sample=f"{sb} of {cfg.batch} sequences ({P} of {cfg.n_prob} (batch, kv-head) problems) per timed pass, "
+                       f"{len(times)} passes, median {per_sample * 1e3:.1f} ms, scaled x{cfg.batch / sb:g}; "
+                       f"C restatement of DataLayer::query (exact scan, fp32 SIMD-shaped dot) + attention, OpenMP"), \
+        per_step
+
+
+def run_reference(args, cfg):
+    """`--impl reference`: the reference's CPU path (restated in C, see oracle/) on the host cores."""
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    if world > 1 and rank != 0:
+        return
+    use_cuda = torch.cuda.is_available()
+    dev = torch.device("cuda", 0) if use_cuda else torch.device("cpu")
+    sb = 2
+    k, v = synth.make_kv(sb, cfg.kv_heads, cfg.context, cfg.head_dim, 1000, cfg.dtype, device=dev)
+    q = synth.make_query(k[:, :, cfg.sink:cfg.sink + cfg.n_retrieval], cfg.group, 1000)
+    sub = synth.StepConfig(cfg.name, cfg.batch, cfg.q_heads, cfg.kv_heads, cfg.head_dim, cfg.context, cfg.topk,
+                           cfg.sink, cfg.window, cfg.dtype)
+    # warm-up passes, then `steps` timed passes (each pass = a bounded sample of the batch)
+    cpu_reference_step_rate(sub, k, v, q, budget_s=0.0, max_steps=max(1, min(args.warmup, 2)), sample_batch=sb)
+    base, per_step = cpu_reference_step_rate(sub, k, v, q, budget_s=60.0, max_steps=max(2, args.steps), sample_batch=sb)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": base["value"], "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_step * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": cfg.dtype, "data": "synthetic",
+        "config": workload_config(cfg, args.gpus), "cpu_baseline": base,
+        "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(cfg, n_gpus):
+    return {
+        "workload": f"{cfg.name}: batch {cfg.batch} x {cfg.q_heads}q/{cfg.kv_heads}kv heads x head_dim {cfg.head_dim}, "
+                    f"context {cfg.context}, top-k {cfg.topk} + {cfg.sink} sink + {cfg.window} window, one layer",
+        "per_gpu_batch": cfg.batch, "global_batch": cfg.batch * n_gpus, "context": cfg.context,
+        "parallelism": f"independent batch replica per GPU x{n_gpus} (no data-path collective)",
+        "l2_policy": "inputs (4.28 GB of keys scanned per step) are larger than L2; no flush needed",
+        "algorithmic_bytes_per_step": cfg.algorithmic_bytes(),
+    }
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="cfg1", choices=sorted(synth.CONFIGS))
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--profile", action="store_true",
+                    help="only the device-resident loop (for profiler captures): no e2e leg, no CPU baseline, "
+                         "no clock sampling, warm-up taken as given")
+    args = ap.parse_args()
+    cfg = synth.CONFIGS[args.workload]
+    if args.impl == "ours" and not args.profile:
+        args.warmup = max(args.warmup, 3)
+
+    if args.impl == "reference":
+        run_reference(args, cfg)
+        return
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the CUDA path has no CPU fallback")
+    world, rank, local = dist_setup(args.gpus)
+    device = torch.device("cuda", local if world > 1 else 0)
+    eng, q, res_k, res_v, res_rows, k_new, v_new, host = build_step_inputs(cfg, 1000 + rank, device)
+    out = torch.empty_like(q)
+    idx = torch.zeros((cfg.batch, cfg.kv_heads, cfg.topk), dtype=torch.int32, device=device)
+
+    def step():
+        eng.decode_attend(q, out, cfg.topk, res_k=res_k, res_v=res_v, res_len=res_rows, k_new=k_new, v_new=v_new,
+                          out_idx=idx)
+
+    def barrier():
+        if world > 1:
+            import torch.distributed as dist
+
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident timing (value) ----
+    for _ in range(args.warmup):
+        step()
+    eng.check_status()
+    sampler = ClockSampler(device.index)
+    barrier()
+    if rank == 0 and not args.profile:
+        sampler.start()
+        time.sleep(0.15)
+    eng.set_phase_timing(args.steps)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    elapsed_ms = e0.elapsed_time(e1)
+    phases = eng.phase_times()
+    eng.set_phase_timing(0)
+
+    if args.profile:
+        if rank == 0:
+            print(json.dumps({"profile_run": True, "workload": cfg.name, "ms_per_step": elapsed_ms / args.steps,
+                              "phases": phases}), flush=True)
+        eng.close()
+        return
+
+    # ---- end to end through the public API with host buffers (e2e) ----
+    q_h = q.cpu().pin_memory()
+    kn_h, vn_h = k_new.cpu().pin_memory(), v_new.cpu().pin_memory()
+    out_h = torch.empty_like(q_h).pin_memory()
+    q_d, kn_d, vn_d = torch.empty_like(q), torch.empty_like(k_new), torch.empty_like(v_new)
+
+    def e2e_step():
+        q_d.copy_(q_h, non_blocking=True)
+        kn_d.copy_(kn_h, non_blocking=True)
+        vn_d.copy_(vn_h, non_blocking=True)
+        eng.decode_attend(q_d, out, cfg.topk, res_k=res_k, res_v=res_v, res_len=res_rows, k_new=kn_d, v_new=vn_d)
+        out_h.copy_(out, non_blocking=True)
+        torch.cuda.current_stream().synchronize()  # the caller consumes the result of every step
+
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    f0.record()
+    for _ in range(args.steps):
+        e2e_step()
+    f1.record()
+    barrier()
+    e2e_ms = f0.elapsed_time(f1)
+    clocks = sampler.stop() if rank == 0 else None
+    eng.check_status()
+
+    # ---- max over ranks ----
+    if world > 1:
+        import torch.distributed as dist
+
+        t = torch.tensor([elapsed_ms, e2e_ms], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        elapsed_ms, e2e_ms = float(t[0]), float(t[1])
+
+    if rank == 0:
+        peak, peak_kind = measured_peaks()
+        ms_per_step = elapsed_ms / args.steps
+        value = world * args.steps / (elapsed_ms * 1e-3)
+        scan_ms = phases["scan_ms"] / max(1, phases["steps"])
+        scan_gbs = cfg.scan_bytes() / (scan_ms * 1e-3) / 1e9 if scan_ms > 0 else 0.0
+        step_gbs = cfg.algorithmic_bytes() / (ms_per_step * 1e-3) / 1e9
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": cfg.dtype, "data": "synthetic", "config": workload_config(cfg, world),
+            "roofline": {
+                "bound": "hbm", "kernel": "score_scan_kernel", "achieved": scan_gbs, "peak": peak, "unit": "GB/s",
+                "frac": scan_gbs / peak, "peak_source": f"MEASURED_PEAKS.json hbm_gbs ({peak_kind})",
+                "frac_of_8tbs_nominal": scan_gbs / 8000.0, "traffic": None,
+                "algorithmic_bytes_per_launch": cfg.scan_bytes(), "avg_launch_ms": scan_ms,
+            },
+            "step_roofline": {"achieved": step_gbs, "frac_of_measured": step_gbs / peak,
+                              "frac_of_8tbs_nominal": step_gbs / 8000.0, "unit": "GB/s",
+                              "algorithmic_bytes_per_step": cfg.algorithmic_bytes()},
+            "phases_ms": {"scan": scan_ms, "select": phases["select_ms"] / max(1, phases["steps"]),
+                          "attend": phases["attend_ms"] / max(1, phases["steps"])},
+            "e2e": {"value": world * args.steps / (e2e_ms * 1e-3), "unit": UNIT,
+                    "h2d_bytes_per_step": int(q_h.numel() * 2 + kn_h.numel() * 2 + vn_h.numel() * 2),
+                    "d2h_bytes_per_step": int(out_h.numel() * 2), "ms_per_step": e2e_ms / args.steps},
+            "gpu_launches": 5 * args.steps,
+            "clocks": clocks,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            base, _ = cpu_reference_step_rate(cfg, host["k"], host["v"], q, budget_s=15.0, max_steps=20, sample_batch=2)
+            line["cpu_baseline"] = base
+        print(json.dumps(line), flush=True)
+    eng.close()
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

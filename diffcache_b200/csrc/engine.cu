@@ -9,6 +9,7 @@
 #include <cmath>
 #include <cstring>
 #include <string>
+#include <vector>
 
 #include "common.cuh"
 
@@ -143,6 +144,8 @@ struct dc_engine {
     uint16_t* stage_k = nullptr;   // lazily allocated staging for host-side dc_query outputs
     uint16_t* stage_v = nullptr;
     int64_t stage_rows = 0;
+    std::vector<cudaEvent_t> phase_events;  // 4 per timed step: before scan, after scan, after select, after attend
+    int phase_cap = 0, phase_count = 0;
 };
 
 namespace {
@@ -183,14 +186,19 @@ int gather_rows(const void* store, int64_t prob_stride, int n_prob, int dim, con
 // scan + select on the engine's own buffers; leaves (bits, ids) of the k best rows per problem in
 // out_bits/out_ids (row stride k).  q: device pointer, q_mode as in dc_score_scan.
 int scan_and_select(dc_engine* e, const void* q, int q_mode, int k, uint32_t id_offset, uint32_t* out_bits,
-                    uint32_t* out_ids, cudaStream_t s) {
+                    uint32_t* out_ids, cudaStream_t s, cudaEvent_t* ev = nullptr) {
     int rc = init_minmax(e, s);
     if (rc) return rc;
+    if (ev) DC_CUDA_TRY(cudaEventRecord(ev[0], s));
     rc = score_scan(e->k, e->prob_stride, e->n_prob, e->ctx_len, e->head_dim, e->dtype, q, q_mode, e->group, e->scores,
                     e->score_stride, e->minmax, s);
     if (rc) return rc;
-    return topk_select(e->scores, nullptr, e->score_stride, e->n_prob, e->ctx_len, k, e->minmax, id_offset, out_bits,
-                       out_ids, k, e->status, s);
+    if (ev) DC_CUDA_TRY(cudaEventRecord(ev[1], s));
+    rc = topk_select(e->scores, nullptr, e->score_stride, e->n_prob, e->ctx_len, k, e->minmax, id_offset, out_bits,
+                     out_ids, k, e->status, s);
+    if (rc) return rc;
+    if (ev) DC_CUDA_TRY(cudaEventRecord(ev[2], s));
+    return DC_OK;
 }
 
 int copy_rows_in(dc_engine* e, const void* src, uint16_t* store, int64_t seq_len, int64_t row0, int64_t stride_b,
@@ -299,6 +307,7 @@ int dc_destroy(dc_engine* e) {
     cudaFree(e->k); cudaFree(e->v); cudaFree(e->scores); cudaFree(e->minmax); cudaFree(e->sel_idx);
     cudaFree(e->sel_bits); cudaFree(e->status); cudaFree(e->att_scratch); cudaFree(e->q_dev);
     cudaFree(e->stage_k); cudaFree(e->stage_v);
+    for (cudaEvent_t ev : e->phase_events) cudaEventDestroy(ev);
     cudaGetLastError();
     delete e;
     return DC_OK;
@@ -466,17 +475,53 @@ int dc_decode_attend(dc_engine* e, const void* q, const void* k_new, const void*
     DC_REQUIRE(k + res_len + (k_new ? 1 : 0) >= 1, "dc_decode_attend: nothing to attend over");
     cudaStream_t s = as_stream(stream);
     int rc;
+    cudaEvent_t* ev = nullptr;
+    if (k > 0 && e->phase_count < e->phase_cap) ev = &e->phase_events[4 * e->phase_count];
     if (k > 0) {
-        rc = scan_and_select(e, q, 1, k, 0u, e->sel_bits, e->sel_idx, s);
+        rc = scan_and_select(e, q, 1, k, 0u, e->sel_bits, e->sel_idx, s, ev);
         if (rc) return rc;
     }
     rc = sparse_attend(e->k, e->v, e->prob_stride, e->ctx_len, e->n_prob, e->kv_heads, e->group, e->head_dim, e->dtype,
                        q, e->sel_idx, k, k, 0, k_new, v_new, res_k, res_v, res_stride_b, res_stride_h, res_len, scale,
                        out, out_lse, nullptr, nullptr, e->att_scratch, s);
     if (rc) return rc;
+    if (ev) {
+        DC_CUDA_TRY(cudaEventRecord(ev[3], s));
+        e->phase_count += 1;
+    }
     if (out_idx && k > 0)
         DC_CUDA_TRY(cudaMemcpyAsync(out_idx, e->sel_idx, static_cast<size_t>(e->n_prob) * k * sizeof(uint32_t),
                                     cudaMemcpyDeviceToDevice, s));
+    return DC_OK;
+}
+
+int dc_set_phase_timing(dc_engine* e, int max_steps) {
+    DC_ENGINE_ENTER(e);
+    DC_REQUIRE(max_steps >= 0 && max_steps <= 100000, "dc_set_phase_timing: max_steps=%d", max_steps);
+    while (static_cast<int>(e->phase_events.size()) < 4 * max_steps) {
+        cudaEvent_t ev;
+        DC_CUDA_TRY(cudaEventCreate(&ev));
+        e->phase_events.push_back(ev);
+    }
+    e->phase_cap = max_steps;
+    e->phase_count = 0;
+    return DC_OK;
+}
+
+int dc_get_phase_times(dc_engine* e, float* scan_ms, float* select_ms, float* attend_ms, int* steps) {
+    DC_ENGINE_ENTER(e);
+    DC_REQUIRE(scan_ms && select_ms && attend_ms && steps, "dc_get_phase_times: null pointer");
+    *scan_ms = *select_ms = *attend_ms = 0.0f;
+    *steps = e->phase_count;
+    for (int i = 0; i < e->phase_count; i++) {
+        cudaEvent_t* ev = &e->phase_events[4 * i];
+        DC_CUDA_TRY(cudaEventSynchronize(ev[3]));
+        float a = 0, b = 0, c = 0;
+        DC_CUDA_TRY(cudaEventElapsedTime(&a, ev[0], ev[1]));
+        DC_CUDA_TRY(cudaEventElapsedTime(&b, ev[1], ev[2]));
+        DC_CUDA_TRY(cudaEventElapsedTime(&c, ev[2], ev[3]));
+        *scan_ms += a; *select_ms += b; *attend_ms += c;
+    }
     return DC_OK;
 }
 

@@ -30,6 +30,7 @@ constexpr int kSelThreads = 1024;
 constexpr int kBins = 4096;
 constexpr int kBinsLog2 = 12;
 constexpr int kCandCap = 2048;
+constexpr int kSelUnroll = 8;   // independent loads in flight per thread
 constexpr int kMaxPasses = 8;  // 64 key bits / 12 bits per pass = 6 passes at most
 
 struct SelCtl {
@@ -157,18 +158,18 @@ topk_select_kernel(const uint32_t* __restrict__ bits, const uint32_t* __restrict
             for (int b = tid; b < kBins; b += kSelThreads) s_hist[b] = 0;
             cluster.sync();  // every histogram is clear before anyone adds to the leader's
 
-            for (int64_t base = begin; base < end; base += kSelThreads * 4) {
-                uint32_t bb[4], ii[4];
-                bool ok[4];
+            for (int64_t base = begin; base < end; base += kSelThreads * kSelUnroll) {
+                uint32_t bb[kSelUnroll], ii[kSelUnroll];
+                bool ok[kSelUnroll];
 #pragma unroll
-                for (int u = 0; u < 4; u++) {
+                for (int u = 0; u < kSelUnroll; u++) {  // all loads of the batch in flight together
                     int64_t i = base + u * kSelThreads + tid;
                     ok[u] = i < end;
                     bb[u] = ok[u] ? pb[i] : 0u;
                     ii[u] = ok[u] ? (pi ? pi[i] : static_cast<uint32_t>(i)) : 0u;
                 }
 #pragma unroll
-                for (int u = 0; u < 4; u++) {
+                for (int u = 0; u < kSelUnroll; u++) {
                     unsigned long long key = (static_cast<unsigned long long>(bb[u]) << 32) | ii[u];
                     if (ok[u] && key >= lo && key <= hi) atomicAdd(&s_hist[(key - lo) >> shift], 1u);
                 }
@@ -213,36 +214,45 @@ topk_select_kernel(const uint32_t* __restrict__ bits, const uint32_t* __restrict
     cluster.sync();  // leader's counters are initialised / nobody still reads ctl.t
     const uint32_t base_out = static_cast<uint32_t>(k_eff) - need;  // keys strictly below lo
     const bool single_value = (lo == hi);
-    for (int64_t base = begin; base < end; base += kSelThreads) {
-        int64_t i = base + tid;
-        bool ok = i < end;
-        uint32_t b = ok ? pb[i] : 0u;
-        uint32_t id = ok ? (pi ? pi[i] : static_cast<uint32_t>(i)) : 0u;
-        unsigned long long key = (static_cast<unsigned long long>(b) << 32) | id;
-        bool emit = ok && (take_all || key < lo);
-        bool tie = ok && !take_all && key >= lo && key <= hi;
-        unsigned em = __ballot_sync(0xFFFFFFFFu, emit);
-        unsigned tm = __ballot_sync(0xFFFFFFFFu, tie);
-        const unsigned lt = (1u << (tid & 31)) - 1u;
-        if (em) {
-            uint32_t wbase = 0;
-            if ((tid & 31) == 0) wbase = atomicAdd(&l_ctl->out_count, __popc(em));
-            wbase = __shfl_sync(0xFFFFFFFFu, wbase, 0);
-            if (emit) {
-                uint32_t pos = wbase + __popc(em & lt);
-                if (pos < static_cast<uint32_t>(kpad)) l_out[pos] = key;
-            }
+    const unsigned lt = (1u << (tid & 31)) - 1u;
+    for (int64_t base = begin; base < end; base += kSelThreads * kSelUnroll) {
+        uint32_t bb[kSelUnroll], ii[kSelUnroll];
+        bool ok[kSelUnroll];
+#pragma unroll
+        for (int u = 0; u < kSelUnroll; u++) {
+            int64_t i = base + u * kSelThreads + tid;
+            ok[u] = i < end;
+            bb[u] = ok[u] ? pb[i] : 0u;
+            ii[u] = ok[u] ? (pi ? pi[i] : static_cast<uint32_t>(i)) : 0u;
         }
-        if (tm) {
-            uint32_t wbase = 0;
-            if ((tid & 31) == 0) wbase = atomicAdd(single_value ? &l_ctl->dup_count : &l_ctl->cand_count, __popc(tm));
-            wbase = __shfl_sync(0xFFFFFFFFu, wbase, 0);
-            if (tie) {
-                uint32_t pos = wbase + __popc(tm & lt);
-                if (single_value) {
-                    if (pos < need) l_out[base_out + pos] = key;
-                } else if (pos < kCandCap) {
-                    l_cand[pos] = key;
+#pragma unroll
+        for (int u = 0; u < kSelUnroll; u++) {
+            const unsigned long long key = (static_cast<unsigned long long>(bb[u]) << 32) | ii[u];
+            const bool emit = ok[u] && (take_all || key < lo);
+            const bool tie = ok[u] && !take_all && key >= lo && key <= hi;
+            const unsigned em = __ballot_sync(0xFFFFFFFFu, emit);
+            const unsigned tm = __ballot_sync(0xFFFFFFFFu, tie);
+            if (em) {  // one shared-memory atomic per warp, positions by prefix popcount
+                uint32_t wbase = 0;
+                if ((tid & 31) == 0) wbase = atomicAdd(&l_ctl->out_count, __popc(em));
+                wbase = __shfl_sync(0xFFFFFFFFu, wbase, 0);
+                if (emit) {
+                    uint32_t pos = wbase + __popc(em & lt);
+                    if (pos < static_cast<uint32_t>(kpad)) l_out[pos] = key;
+                }
+            }
+            if (tm) {
+                uint32_t wbase = 0;
+                if ((tid & 31) == 0)
+                    wbase = atomicAdd(single_value ? &l_ctl->dup_count : &l_ctl->cand_count, __popc(tm));
+                wbase = __shfl_sync(0xFFFFFFFFu, wbase, 0);
+                if (tie) {
+                    uint32_t pos = wbase + __popc(tm & lt);
+                    if (single_value) {
+                        if (pos < need) l_out[base_out + pos] = key;
+                    } else if (pos < kCandCap) {
+                        l_cand[pos] = key;
+                    }
                 }
             }
         }

@@ -262,6 +262,18 @@ class DiffCacheGPU:
                                               sh, int(res_len), int(topk), float(scale), _ptr(out), _ptr(out_idx),
                                               _ptr(out_lse), _current_stream(stream)))
 
+    def set_phase_timing(self, max_steps: int) -> None:
+        """Record CUDA events around the scan / select / attend phases of the next ``max_steps``
+        ``decode_attend`` calls (the counterpart of the reference's per-layer latency counters)."""
+        _lib.check(self._lib.dc_set_phase_timing(self._h, int(max_steps)))
+
+    def phase_times(self) -> dict:
+        """Summed milliseconds per phase over the recorded steps."""
+        a, b, c, n = ctypes.c_float(), ctypes.c_float(), ctypes.c_float(), ctypes.c_int()
+        _lib.check(self._lib.dc_get_phase_times(self._h, ctypes.byref(a), ctypes.byref(b), ctypes.byref(c),
+                                                ctypes.byref(n)))
+        return {"steps": n.value, "scan_ms": a.value, "select_ms": b.value, "attend_ms": c.value}
+
     def local_topk(self, q, topk: int, out_bits, out_gidx, stream=None) -> None:
         _lib.check(self._lib.dc_local_topk(self._h, _ptr(q), int(topk), _ptr(out_bits), _ptr(out_gidx),
                                            _current_stream(stream)))

@@ -54,6 +54,9 @@ class StepConfig:
 CONFIGS = {
     "cfg0": StepConfig("cfg0", 1, 32, 8, 128, 32768, 1024, 64, 256, "fp16"),
     "cfg1": StepConfig("cfg1", 16, 32, 8, 128, 131072, 2048, 64, 512, "bf16"),
+    # configuration 1 with two sequences: same kernels and per-problem sizes, 0.5 GB of keys (still larger
+    # than L2) — the case profiler captures are taken on
+    "cfg1_b2": StepConfig("cfg1_b2", 2, 32, 8, 128, 131072, 2048, 64, 512, "bf16"),
     "cfg2_layer": StepConfig("cfg2_layer", 8, 32, 8, 128, 131072, 2048, 64, 512, "bf16"),
     "cfg3": StepConfig("cfg3", 1, 32, 8, 128, 1048576, 4096, 64, 1024, "bf16"),
     "cfg4": StepConfig("cfg4", 4, 32, 8, 128, 262144, 2048, 0, 0, "bf16"),

@@ -174,6 +174,19 @@ int dc_decode_attend(dc_engine* e, const void* q, const void* k_new, const void*
                      int res_len, int topk, float scale, void* out, int32_t* out_idx,
                      float* out_lse, uint64_t stream);
 
+/*
+ * Per-phase device timing of dc_decode_attend, the counterpart of the reference's
+ * `{name}_search_latency` / `{name}_collect_latency` / `{name}_total_query_latency`
+ * counters (diffcache_cpu/src/nsw.rs:618,660, diffcache_cpu/src/lib.rs:403).
+ * dc_set_phase_timing(e, n) makes the next n calls of dc_decode_attend record CUDA
+ * events on their stream around the scan, select and attend phases (n = 0 turns
+ * it off; not usable while the stream is being captured into a graph).
+ * dc_get_phase_times synchronises those events and returns the SUM in milliseconds
+ * of each phase over the `*steps` recorded calls.
+ */
+int dc_set_phase_timing(dc_engine* e, int max_steps);
+int dc_get_phase_times(dc_engine* e, float* scan_ms, float* select_ms, float* attend_ms, int* steps);
+
 /* ------------------------------------------------------------------------- *
  * Sequence-sharded decode (one engine per GPU holds a contiguous row range).
  * No counterpart in the reference (single GPU); the semantics are those of the

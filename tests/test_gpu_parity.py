@@ -279,14 +279,53 @@ def test_fused_decode_step_matches_oracle(oracle_lib, dtype, G, D):
         util.u16(v_new).reshape(P, D), D ** -0.5, dt)
     gi = idx.cpu().numpy().reshape(P, -1)
     subs = sum(util.check_selection_parity(gi[p], ref["idx"][p], ref["all_bits"][p]) for p in range(P))
-    got = oracle_lib.to_f32(util.u16(out).reshape(P * G, D), dt)
     if subs == 0:
-        assert np.allclose(got, ref["out_f32"], rtol=RTOL, atol=ATOL)
+        util.assert_attention_close(util.u16(out).reshape(P * G, D), ref["out_f32"], dt, oracle_lib, ATOL, RTOL)
         assert np.allclose(lse.cpu().numpy().reshape(-1), ref["lse"], rtol=1e-4, atol=1e-4)
     # the new token was appended in place (what flash_attn_with_kvcache does, base.py:134-142)
     assert torch.equal(rk[:, :, res_rows].cpu(), k_new) and torch.equal(rv[:, :, res_rows].cpu(), v_new)
     assert torch.equal(rk[:, :, :res_rows].cpu(), res_k[:, :, :res_rows])
     eng.close()
+
+
+@pytest.mark.parametrize("G,D,n_sel", [(4, 128, 700), (7, 128, 33), (1, 64, 1), (2, 256, 2048)])
+def test_sparse_attend_fp32_partials(lib, oracle_lib, G, D, n_sel):
+    """The stateless attention kernel with un-normalised fp32 outputs (what sequence-sharded ranks
+    exchange) against the fp64 oracle, at a tolerance far below the 16-bit output rounding; ids
+    outside the owned row range and 0xFFFFFFFF pads must be skipped."""
+    B, Hkv, n = 2, 2, 4000
+    P = B * Hkv
+    k, v, q = util.small_problem(B, Hkv, G, n, D, seed=81)
+    rng = np.random.default_rng(82)
+    base = 1000  # this "rank" owns global rows [1000, 1000 + n)
+    own = np.stack([rng.permutation(n)[:n_sel] for _ in range(P)]).astype(np.uint32)
+    sel = np.concatenate([own + base, rng.integers(0, base, (P, 5)).astype(np.uint32),
+                          np.full((P, 3), 0xFFFFFFFF, np.uint32), (own[:, :2] + base + n)], axis=1)
+    sel = np.ascontiguousarray(sel[:, rng.permutation(sel.shape[1])])
+    kd, vd, qd = k.cuda().reshape(P, n, D), v.cuda().reshape(P, n, D), q.cuda()
+    seld = _dev(sel.view(np.int32))
+    acc = torch.zeros((P * G, D), dtype=torch.float32, device="cuda")
+    ml = torch.zeros((P * G, 2), dtype=torch.float32, device="cuda")
+    scratch = torch.zeros(int(lib.dc_attend_scratch_bytes(P, G, D)), dtype=torch.uint8, device="cuda")
+    rc = lib.dc_sparse_attend(kd.data_ptr(), vd.data_ptr(), n * D, n, P, Hkv, G, D, 0, qd.data_ptr(), seld.data_ptr(),
+                              sel.shape[1], sel.shape[1], base, None, None, None, None, 0, 0, 0, 0.0, None, None,
+                              acc.data_ptr(), ml.data_ptr(), scratch.data_ptr(), _stream())
+    assert rc == 0, lib.dc_last_error()
+    torch.cuda.synchronize()
+    ku, vu = util.u16(k).reshape(P, n, D), util.u16(v).reshape(P, n, D)
+    kk = np.stack([ku[p][own[p]] for p in range(P)])
+    vv = np.stack([vu[p][own[p]] for p in range(P)])
+    of, _, lse = oracle_lib.attend(kk, vv, util.u16(q).reshape(P * G, D), G, D ** -0.5, 0)
+    a, m = acc.cpu().numpy(), ml.cpu().numpy()
+    assert np.allclose(a / m[:, 1:2], of, rtol=2e-4, atol=2e-5)
+    assert np.allclose((m[:, 0] + np.log2(m[:, 1])) * np.log(2.0), lse, rtol=1e-5, atol=1e-4)
+    # merging partials laid out (part, row, D), as an all-gather delivers them
+    out = torch.zeros((P * G, D), dtype=torch.bfloat16, device="cuda")
+    acc2 = torch.stack([acc, acc * 0, acc]).contiguous()
+    ml2 = torch.stack([ml, torch.tensor([float("-inf"), 0.0], device="cuda").expand_as(ml), ml]).contiguous()
+    assert lib.dc_lse_combine(acc2.data_ptr(), ml2.data_ptr(), 3, P * G, D, 0, out.data_ptr(), None, _stream()) == 0
+    torch.cuda.synchronize()
+    util.assert_attention_close(util.u16(out), of, 0, oracle_lib, ATOL, RTOL)
 
 
 def test_fused_step_edge_cases(oracle_lib):
@@ -305,7 +344,7 @@ def test_fused_step_edge_cases(oracle_lib):
     of, _, _ = oracle_lib.attend(util.u16(k).reshape(P, 300, D), util.u16(v).reshape(P, 300, D),
                                  util.u16(q).reshape(P * G, D), G, scale, 0)
     assert sorted(idx.cpu().numpy()[0, 0].tolist()) == list(range(300))
-    assert np.allclose(oracle_lib.to_f32(util.u16(out).reshape(P * G, D), 0), of, rtol=RTOL, atol=ATOL)
+    util.assert_attention_close(util.u16(out).reshape(P * G, D), of, 0, oracle_lib, ATOL, RTOL)
     eng.close()
     # (b) empty store: attention over resident rows + new token only
     eng = DiffCacheGPU(B, Hkv * G, Hkv, D, max_ctx_len=16)
@@ -316,7 +355,7 @@ def test_fused_step_edge_cases(oracle_lib):
     out, _, _ = _run_decode(eng, qd, rk, rv, 30, kn, vn, 2048)
     of, _, _ = oracle_lib.attend(util.u16(k[:, :, :31]).reshape(P, 31, D), util.u16(v[:, :, :31]).reshape(P, 31, D),
                                  util.u16(q).reshape(P * G, D), G, scale, 0)
-    assert np.allclose(oracle_lib.to_f32(util.u16(out).reshape(P * G, D), 0), of, rtol=RTOL, atol=ATOL)
+    util.assert_attention_close(util.u16(out).reshape(P * G, D), of, 0, oracle_lib, ATOL, RTOL)
     # (c) nothing at all to attend over is an argument error, not a crash
     from diffcache_b200 import DiffCacheError
     with pytest.raises(DiffCacheError):
@@ -367,7 +406,7 @@ def test_kvcache_manager_flow(oracle_lib):
         out = cache.decode_attention(l, q, kn, vn)
         torch.cuda.synchronize()
         if all(same):
-            assert np.allclose(oracle_lib.to_f32(util.u16(out).reshape(P * G, D), 0), of, rtol=RTOL, atol=ATOL)
+            util.assert_attention_close(util.u16(out).reshape(P * G, D), of, 0, oracle_lib, ATOL, RTOL)
         else:  # an ulp tie at the boundary: the fused path must still agree with the three-call path
             assert sum(same) >= P - 1
     assert cache.kvbuf_suffix_len == suffix + 1

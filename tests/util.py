@@ -76,3 +76,17 @@ def small_problem(batch, kv_heads, group, n, head_dim, seed, dtype="bf16", devic
     k, v = synth.make_kv(batch, kv_heads, n, head_dim, seed, dtype, device=device)
     q = synth.make_query(k, group, seed) if n > 0 else torch.randn(batch, kv_heads * group, head_dim).to(k.dtype)
     return k, v, q
+
+
+def assert_attention_close(got_u16, want_f32, dtype, oracle, atol=1e-3, rtol=2e-3):
+    """Output tolerance of the task (2e-3 relative / 1e-3 absolute) applied to the value the
+    kernel computed; the final rounding to a 16-bit type can add up to half a unit in the last
+    place of that type on top (2^-9 relative for bf16, 2^-12 for fp16), which no kernel can avoid."""
+    got = oracle.to_f32(np.ascontiguousarray(got_u16), dtype).astype(np.float64)
+    want = want_f32.astype(np.float64)
+    mant = 8 if dtype == 0 else 11
+    with np.errstate(divide="ignore"):
+        half_ulp = np.where(want == 0, 0.0, 2.0 ** (np.floor(np.log2(np.abs(want) + 1e-300)) - mant))
+    tol = atol + rtol * np.abs(want) + half_ulp
+    bad = np.abs(got - want) > tol
+    assert not bad.any(), f"{bad.sum()} outputs off; worst {np.max(np.abs(got - want) - tol):.3e} beyond tolerance"

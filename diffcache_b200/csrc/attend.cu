@@ -10,6 +10,7 @@
 // is split over several CTAs whose (max, sum, accumulator) partials are merged by
 // log-sum-exp in a second small kernel.
 #include <cmath>
+#include <cstdlib>
 
 #include "common.cuh"
 
@@ -71,7 +72,7 @@ sparse_attend_kernel(const AttendArgs a) {
     __shared__ const uint16_t* s_vptr[TILE];
     __shared__ float s_p[GC][TILE];
     __shared__ float s_alpha[GC], s_m[GC], s_l[GC];
-    __shared__ float s_red[NRG][GC][D + 4];
+    __shared__ __align__(16) float s_red[NRG][GC][D + 4];  // written with 16-byte stores
 
     const int has_new = a.k_new != nullptr ? 1 : 0;
     const int total = a.n_sel + a.res_len + has_new;
@@ -305,8 +306,13 @@ int launch_attend(const AttendArgs& a, int n_prob, cudaStream_t stream) {
 }  // namespace
 
 int attend_splits(int n_prob, int total_rows) {
-    // about four CTAs per SM over the whole grid, at least 32 rows per split
-    int target = (4 * sm_count() + n_prob - 1) / std::max(1, n_prob);
+    // about kCtasPerSm CTAs per SM over the whole grid, at least 32 rows per split
+    static const int per_sm = [] {
+        const char* s = std::getenv("DC_ATTEND_CTAS_PER_SM");
+        int v = (s && *s) ? std::atoi(s) : 4;
+        return std::min(std::max(v, 1), 4);  // the scratch buffer is sized for at most 4 per SM
+    }();
+    int target = (per_sm * sm_count() + n_prob - 1) / std::max(1, n_prob);
     int by_rows = std::max(1, (total_rows + 31) / 32);
     return std::max(1, std::min(std::min(target, by_rows), 256));
 }

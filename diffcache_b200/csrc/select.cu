@@ -30,7 +30,7 @@ constexpr int kSelThreads = 1024;
 constexpr int kBins = 4096;
 constexpr int kBinsLog2 = 12;
 constexpr int kCandCap = 2048;
-constexpr int kSelUnroll = 8;   // independent loads in flight per thread
+constexpr int kSelUnroll = 4;   // independent loads in flight per thread
 constexpr int kMaxPasses = 8;  // 64 key bits / 12 bits per pass = 6 passes at most
 
 struct SelCtl {
@@ -81,6 +81,51 @@ __device__ __forceinline__ void bitonic_sort_u64(unsigned long long* a, int n) {
     }
 }
 
+// atomicAdd(counter, 1) for every currently active lane with ONE atomic per warp: the lanes that
+// reach this point together elect a leader, which reserves popc(active) slots.
+__device__ __forceinline__ uint32_t warp_aggregated_inc(uint32_t* counter) {
+    const unsigned active = __activemask();
+    const int lane = threadIdx.x & 31;
+    const int leader = __ffs(active) - 1;
+    uint32_t base = 0;
+    if (lane == leader) base = atomicAdd(counter, static_cast<uint32_t>(__popc(active)));
+    base = __shfl_sync(active, base, leader);
+    return base + __popc(active & ((1u << lane) - 1u));
+}
+
+// Calls f(bits, position) for every score of [begin, end).  16-byte loads, kSelUnroll of them in
+// flight per thread, when the slice is 16-byte aligned; scalar loads otherwise and for the tail.
+template <class F>
+__device__ __forceinline__ void for_each_score(const uint32_t* __restrict__ pb, int64_t begin, int64_t end, F&& f) {
+    const uint32_t tid = threadIdx.x;
+    const uint32_t n = static_cast<uint32_t>(end - begin);
+    const uint32_t first = static_cast<uint32_t>(begin);
+    const uint32_t* p = pb + begin;
+    uint32_t done = 0;
+    if ((reinterpret_cast<uintptr_t>(p) & 15) == 0) {
+        const uint32_t nvec = n >> 2;
+        const uint4* pv = reinterpret_cast<const uint4*>(p);
+        for (uint32_t v0 = 0; v0 < nvec; v0 += kSelThreads * kSelUnroll) {
+            uint4 w[kSelUnroll];
+#pragma unroll
+            for (int u = 0; u < kSelUnroll; u++) {
+                const uint32_t v = v0 + u * kSelThreads + tid;
+                if (v < nvec) w[u] = pv[v];
+            }
+#pragma unroll
+            for (int u = 0; u < kSelUnroll; u++) {
+                const uint32_t v = v0 + u * kSelThreads + tid;
+                if (v < nvec) {
+                    const uint32_t i = first + 4 * v;
+                    f(w[u].x, i); f(w[u].y, i + 1); f(w[u].z, i + 2); f(w[u].w, i + 3);
+                }
+            }
+        }
+        done = nvec << 2;
+    }
+    for (uint32_t i = done + tid; i < n; i += kSelThreads) f(p[i], first + i);
+}
+
 // grid = (cluster_size, n_prob), cluster = (cluster_size, 1, 1).
 // dynamic shared memory: out[kpad] u64 | cand[kCandCap] u64 | hist[kBins] u32
 __global__ void __launch_bounds__(kSelThreads, 1)
@@ -110,8 +155,9 @@ topk_select_kernel(const uint32_t* __restrict__ bits, const uint32_t* __restrict
     const uint32_t* pb = bits + prob * in_stride;
     const uint32_t* pi = ids ? ids + prob * in_stride : nullptr;
 
-    // slice of the problem this CTA reads
+    // slice of the problem this CTA reads (a multiple of 4 scores so that slices stay 16-byte aligned)
     int64_t per = (n + csize - 1) / csize;
+    per = (per + 3) & ~static_cast<int64_t>(3);
     const int64_t begin = min(n, static_cast<int64_t>(rank) * per);
     const int64_t end = min(n, begin + per);
 
@@ -127,6 +173,11 @@ topk_select_kernel(const uint32_t* __restrict__ bits, const uint32_t* __restrict
     uint32_t need = static_cast<uint32_t>(k_eff);
     const bool take_all = (k_eff == n);
 
+    auto key_of = [&](uint32_t b, uint32_t i) -> unsigned long long {
+        const uint32_t id = pi ? pi[i] : i;
+        return (static_cast<unsigned long long>(b) << 32) | id;
+    };
+
     if (!take_all) {
         // ---- key range ----
         uint32_t mn, mx;
@@ -136,10 +187,7 @@ topk_select_kernel(const uint32_t* __restrict__ bits, const uint32_t* __restrict
         } else {
             cluster.sync();  // leader's ctl initialised
             mn = 0xFFFFFFFFu; mx = 0u;
-            for (int64_t i = begin + tid; i < end; i += kSelThreads) {
-                uint32_t b = pb[i];
-                mn = min(mn, b); mx = max(mx, b);
-            }
+            for_each_score(pb, begin, end, [&](uint32_t b, uint32_t) { mn = min(mn, b); mx = max(mx, b); });
             mn = __reduce_min_sync(0xFFFFFFFFu, mn);
             mx = __reduce_max_sync(0xFFFFFFFFu, mx);
             if ((tid & 31) == 0) { atomicMin(&l_ctl->mn, mn); atomicMax(&l_ctl->mx, mx); }
@@ -158,21 +206,25 @@ topk_select_kernel(const uint32_t* __restrict__ bits, const uint32_t* __restrict
             for (int b = tid; b < kBins; b += kSelThreads) s_hist[b] = 0;
             cluster.sync();  // every histogram is clear before anyone adds to the leader's
 
-            for (int64_t base = begin; base < end; base += kSelThreads * kSelUnroll) {
-                uint32_t bb[kSelUnroll], ii[kSelUnroll];
-                bool ok[kSelUnroll];
-#pragma unroll
-                for (int u = 0; u < kSelUnroll; u++) {  // all loads of the batch in flight together
-                    int64_t i = base + u * kSelThreads + tid;
-                    ok[u] = i < end;
-                    bb[u] = ok[u] ? pb[i] : 0u;
-                    ii[u] = ok[u] ? (pi ? pi[i] : static_cast<uint32_t>(i)) : 0u;
-                }
-#pragma unroll
-                for (int u = 0; u < kSelUnroll; u++) {
-                    unsigned long long key = (static_cast<unsigned long long>(bb[u]) << 32) | ii[u];
-                    if (ok[u] && key >= lo && key <= hi) atomicAdd(&s_hist[(key - lo) >> shift], 1u);
-                }
+            const uint32_t lo32 = static_cast<uint32_t>(lo >> 32), hi32 = static_cast<uint32_t>(hi >> 32);
+            // Bins depend on the dist bits alone while the range still spans whole ids (always true on
+            // the first pass): then this is pure 32-bit work and the ids are never read.
+            const bool bits_only = (static_cast<uint32_t>(lo) == 0u) && (static_cast<uint32_t>(hi) == 0xFFFFFFFFu) &&
+                                   shift >= 32;
+            if (bits_only) {
+                const uint32_t span = hi32 - lo32;
+                const int sh = shift - 32;
+                for_each_score(pb, begin, end, [&](uint32_t b, uint32_t) {
+                    const uint32_t d = b - lo32;
+                    if (d <= span) atomicAdd(&s_hist[d >> sh], 1u);
+                });
+            } else {
+                for_each_score(pb, begin, end, [&](uint32_t b, uint32_t i) {
+                    if (b >= lo32 && b <= hi32) {
+                        const unsigned long long key = key_of(b, i);
+                        if (key >= lo && key <= hi) atomicAdd(&s_hist[(key - lo) >> shift], 1u);
+                    }
+                });
             }
             __syncthreads();
             if (rank != 0) {
@@ -214,48 +266,31 @@ topk_select_kernel(const uint32_t* __restrict__ bits, const uint32_t* __restrict
     cluster.sync();  // leader's counters are initialised / nobody still reads ctl.t
     const uint32_t base_out = static_cast<uint32_t>(k_eff) - need;  // keys strictly below lo
     const bool single_value = (lo == hi);
-    const unsigned lt = (1u << (tid & 31)) - 1u;
-    for (int64_t base = begin; base < end; base += kSelThreads * kSelUnroll) {
-        uint32_t bb[kSelUnroll], ii[kSelUnroll];
-        bool ok[kSelUnroll];
-#pragma unroll
-        for (int u = 0; u < kSelUnroll; u++) {
-            int64_t i = base + u * kSelThreads + tid;
-            ok[u] = i < end;
-            bb[u] = ok[u] ? pb[i] : 0u;
-            ii[u] = ok[u] ? (pi ? pi[i] : static_cast<uint32_t>(i)) : 0u;
-        }
-#pragma unroll
-        for (int u = 0; u < kSelUnroll; u++) {
-            const unsigned long long key = (static_cast<unsigned long long>(bb[u]) << 32) | ii[u];
-            const bool emit = ok[u] && (take_all || key < lo);
-            const bool tie = ok[u] && !take_all && key >= lo && key <= hi;
-            const unsigned em = __ballot_sync(0xFFFFFFFFu, emit);
-            const unsigned tm = __ballot_sync(0xFFFFFFFFu, tie);
-            if (em) {  // one shared-memory atomic per warp, positions by prefix popcount
-                uint32_t wbase = 0;
-                if ((tid & 31) == 0) wbase = atomicAdd(&l_ctl->out_count, __popc(em));
-                wbase = __shfl_sync(0xFFFFFFFFu, wbase, 0);
-                if (emit) {
-                    uint32_t pos = wbase + __popc(em & lt);
-                    if (pos < static_cast<uint32_t>(kpad)) l_out[pos] = key;
+    if (take_all) {
+        for_each_score(pb, begin, end, [&](uint32_t b, uint32_t i) {
+            const uint32_t pos = warp_aggregated_inc(&l_ctl->out_count);
+            if (pos < static_cast<uint32_t>(kpad)) l_out[pos] = key_of(b, i);
+        });
+    } else {
+        // Winners are ~k of n scores, so a 32-bit pre-test on the dist bits rejects almost every
+        // element before its id is looked at; positions come from one shared-memory atomic each.
+        const uint32_t hi32 = static_cast<uint32_t>(hi >> 32);
+        for_each_score(pb, begin, end, [&](uint32_t b, uint32_t i) {
+            if (b > hi32) return;
+            const unsigned long long key = key_of(b, i);
+            if (key < lo) {
+                const uint32_t pos = warp_aggregated_inc(&l_ctl->out_count);
+                if (pos < static_cast<uint32_t>(kpad)) l_out[pos] = key;
+            } else if (key <= hi) {
+                if (single_value) {
+                    const uint32_t pos = atomicAdd(&l_ctl->dup_count, 1u);
+                    if (pos < need) l_out[base_out + pos] = key;
+                } else {
+                    const uint32_t pos = atomicAdd(&l_ctl->cand_count, 1u);
+                    if (pos < kCandCap) l_cand[pos] = key;
                 }
             }
-            if (tm) {
-                uint32_t wbase = 0;
-                if ((tid & 31) == 0)
-                    wbase = atomicAdd(single_value ? &l_ctl->dup_count : &l_ctl->cand_count, __popc(tm));
-                wbase = __shfl_sync(0xFFFFFFFFu, wbase, 0);
-                if (tie) {
-                    uint32_t pos = wbase + __popc(tm & lt);
-                    if (single_value) {
-                        if (pos < need) l_out[base_out + pos] = key;
-                    } else if (pos < kCandCap) {
-                        l_cand[pos] = key;
-                    }
-                }
-            }
-        }
+        });
     }
     cluster.sync();  // all remote writes into the leader have landed
     if (rank != 0) return;

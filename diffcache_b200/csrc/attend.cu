@@ -409,3 +409,78 @@ int sparse_attend(const void* k_store, const void* v_store, int64_t prob_stride,
 }
 
 }  // namespace dc
+
+// ---------------------------------------------------------------------------------------------
+// Sparse attention for callers that cannot allocate device memory.
+//
+// Some hosts of this library hand the whole of HBM to their own pool at start-up (inference
+// servers do) or forbid cudaMalloc once they are serving, because it synchronises the device.
+// Such a caller cannot provide the split-K scratch buffer dc_sparse_attend asks for, so this
+// variant keeps the scratch in a fixed array that is part of the library image: every GPU that
+// loads the library holds DC_NOALLOC_SCRATCH_BYTES (4 MiB) of it until the process exits.
+//
+// The array's name is only a host-side handle; the device address is looked up once per device
+// with cudaGetSymbolAddress (with that device current) by the FIRST call on that device, so the
+// first call on a device should be made before any stream capture.  Later calls only launch
+// kernels.  Nothing here calls cudaMalloc, cudaFree or any allocating routine.
+//
+// All calls on a device share the one array.  It keeps whatever the previous call left there;
+// that is harmless because the attention kernel writes every partial slot (accumulator, max,
+// sum — empty splits included) before the merge kernel of the same call reads it, so nothing has
+// to start at zero.  Two calls whose kernels overlap on the GPU (different streams, or graphs
+// replayed concurrently) race on the array and must be serialised by the caller.
+namespace dc {
+namespace {
+
+constexpr size_t kNoAllocScratchBytes = DC_NOALLOC_SCRATCH_BYTES;
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
+
+// Device address of g_noalloc_scratch on the current device (nullptr + error code on failure).
+int noalloc_scratch_ptr(void** out) {
+    static void* ptrs[64] = {};
+    static bool ready[64] = {};
+    *out = nullptr;
+    int dev = 0;
+    DC_CUDA_TRY(cudaGetDevice(&dev));
+    DC_REQUIRE(dev >= 0 && dev < 64, "dc_sparse_attend_noalloc: device ordinal %d not supported", dev);
+    if (!ready[dev]) {
+        void* p = nullptr;
+        DC_CUDA_TRY(cudaGetSymbolAddress(&p, g_noalloc_scratch));
+        DC_REQUIRE(p != nullptr, "dc_sparse_attend_noalloc: no device address for the static scratch array");
+        ptrs[dev] = p;
+        ready[dev] = true;
+    }
+    *out = ptrs[dev];
+    return DC_OK;
+}
+
+}  // namespace
+}  // namespace dc
+
+extern "C" int dc_sparse_attend_noalloc(const void* k_store, const void* v_store, int64_t prob_stride, int64_t n_rows,
+                                        int n_prob, int kv_heads, int group, int head_dim, int dtype, const void* q,
+                                        const uint32_t* sel, int64_t sel_stride, int n_sel, int64_t sel_base,
+                                        const void* k_new, const void* v_new, void* res_k, void* res_v,
+                                        int64_t res_stride_b, int64_t res_stride_h, int res_len, float scale,
+                                        void* out, float* out_lse, float* out_acc, float* out_ml, uint64_t stream) {
+    using namespace dc;
+    DC_REQUIRE(n_prob >= 0 && n_prob <= 65535 && group >= 1 && group <= 64 && n_sel >= 0 && res_len >= 0,
+               "dc_sparse_attend_noalloc: bad sizes");
+    DC_REQUIRE(head_dim == 64 || head_dim == 128 || head_dim == 256,
+               "dc_sparse_attend_noalloc: head_dim %d not in {64,128,256}", head_dim);
+    const int total = n_sel + res_len + (k_new ? 1 : 0);
+    const int64_t need = static_cast<int64_t>(n_prob) * attend_splits(n_prob, total) * group * (head_dim + 2) *
+                         static_cast<int64_t>(sizeof(float));
+    if (need > static_cast<int64_t>(kNoAllocScratchBytes)) {
+        set_error("dc_sparse_attend_noalloc: this problem needs %lld bytes of split-K scratch but the static array "
+                  "holds %lld (DC_NOALLOC_SCRATCH_BYTES); use dc_sparse_attend with a caller-provided buffer",
+                  static_cast<long long>(need), static_cast<long long>(kNoAllocScratchBytes));
+        return DC_EINVAL;
+    }
+    void* scratch = nullptr;
+    int rc = noalloc_scratch_ptr(&scratch);
+    if (rc != DC_OK) return rc;
+    return sparse_attend(k_store, v_store, prob_stride, n_rows, n_prob, kv_heads, group, head_dim, dtype, q, sel,
+                         sel_stride, n_sel, sel_base, k_new, v_new, res_k, res_v, res_stride_b, res_stride_h, res_len,
+                         scale, out, out_lse, out_acc, out_ml, scratch, as_stream(stream));
+}

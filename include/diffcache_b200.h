@@ -270,6 +270,31 @@ int dc_sparse_attend(const void* k_store, const void* v_store, int64_t prob_stri
 int64_t dc_attend_scratch_bytes(int n_prob, int group, int head_dim);
 
 /*
+ * dc_sparse_attend for callers that cannot allocate device memory (no
+ * counterpart in the reference).  A host that gives all of HBM to its own pool
+ * at start-up, or that may not call cudaMalloc while serving because it
+ * synchronises the device, has no buffer to pass as `scratch`; here the split-K
+ * scratch is a fixed DC_NOALLOC_SCRATCH_BYTES array inside the library image
+ * (held by every GPU that loads the library until the process exits), and the
+ * call allocates nothing.  Arguments and results are those of dc_sparse_attend
+ * without `scratch`.  Problems whose partials do not fit are rejected with
+ * DC_EINVAL and a message naming both sizes (the need is
+ * n_prob * splits * group * (head_dim + 2) * 4 bytes, with splits chosen so that
+ * n_prob * splits is about four CTAs per SM).  The first call on a device looks
+ * the array's device address up and should therefore come before any stream
+ * capture.  All calls on a device share the array: calls whose kernels overlap
+ * on the GPU race and must be serialised by the caller; stale contents from an
+ * earlier call are harmless (every slot is written before it is read).
+ */
+#define DC_NOALLOC_SCRATCH_BYTES (4 * 1024 * 1024)
+int dc_sparse_attend_noalloc(const void* k_store, const void* v_store, int64_t prob_stride, int64_t n_rows,
+                             int n_prob, int kv_heads, int group, int head_dim, int dtype, const void* q,
+                             const uint32_t* sel, int64_t sel_stride, int n_sel, int64_t sel_base,
+                             const void* k_new, const void* v_new, void* res_k, void* res_v,
+                             int64_t res_stride_b, int64_t res_stride_h, int res_len, float scale,
+                             void* out, float* out_lse, float* out_acc, float* out_ml, uint64_t stream);
+
+/*
  * Log-sum-exp merge of `n_part` partial results laid out as
  * acc (n_part, rows, head_dim) fp32 and ml (n_part, rows, 2) fp32 into
  * out (rows, head_dim) in the element type and optional lse (rows) fp32.

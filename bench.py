@@ -209,6 +209,70 @@ def run_reference(args, cfg):
     print(json.dumps(line), flush=True)
 
 
+def run_seq_sharded(cfg, world, rank, device, steps, warmup):
+    """Configuration 3: ONE long sequence, retrieval region sharded by rows over the ranks (strong
+    scaling).  Local scan + top-k per rank, all-gather of candidates, identical merge select,
+    attention over owned rows, all-gather of partials, log-sum-exp merge.  Returns a dict (rank 0)."""
+    import torch.distributed as dist
+
+    from diffcache_b200 import DiffCacheGPU, sharded
+
+    dt = synth.torch_dtype(cfg.dtype)
+    n_r = cfg.n_retrieval
+    start, length = sharded.shard_rows(n_r, world)[rank]
+    eng = DiffCacheGPU(cfg.batch, cfg.q_heads, cfg.kv_heads, cfg.head_dim, max_ctx_len=max(length, 1), dtype=cfg.dtype,
+                       device=device.index, use_bruteforce=True)
+    k, v = synth.make_kv(cfg.batch, cfg.kv_heads, length, cfg.head_dim, 3000 + rank, cfg.dtype, device=device,
+                         pos_offset=cfg.sink + start, total=cfg.context)
+    eng.prefill(k, v)
+    q = synth.make_query(k, cfg.group, 3000).contiguous()
+    if world > 1:
+        dist.broadcast(q, src=0)
+    res_k = res_v = k_new = v_new = None
+    res_len = 0
+    if rank == 0 or rank == world - 1:
+        rows = (cfg.sink if rank == 0 else 0) + (cfg.window - 1 if rank == world - 1 else 0)
+        rk, rv = synth.make_kv(cfg.batch, cfg.kv_heads, rows + 9, cfg.head_dim, 4000 + rank, cfg.dtype, device=device)
+        res_k, res_v, res_len = rk, rv, rows
+        if rank == world - 1:
+            k_new, v_new = rk[:, :, -1].contiguous(), rv[:, :, -1].contiguous()
+    del k, v
+    backend = sharded.GpuShardBackend(eng, start, res_k, res_v, res_len, k_new, v_new)
+    step = sharded.SequenceShardedStep(backend, cfg.topk)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(warmup, 3)):
+        step.step(q)
+    eng.check_status()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        out = step.step(q)
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t[0])
+    checksum = float(out.float().abs().sum())
+    eng.close()
+    peak, _ = measured_peaks()
+    per_step = ms / steps
+    gbs = cfg.algorithmic_bytes() / (per_step * 1e-3) / 1e9
+    return {"workload": f"{cfg.name}: batch 1, context {cfg.context}, top-k {cfg.topk} + {cfg.sink} sink + {cfg.window} "
+                        f"window, rows sharded over {world} GPU(s)",
+            "value": 1e3 / per_step, "unit": UNIT, "ms_per_step": per_step, "scaling": "strong", "n_gpus": world,
+            "algorithmic_bytes_per_step": cfg.algorithmic_bytes(), "aggregate_gbs": gbs,
+            "frac_of_measured_hbm_x_gpus": gbs / (peak * world), "collectives_per_step": 0 if world == 1 else 3,
+            "out_checksum": checksum}
+
+
 def workload_config(cfg, n_gpus):
     return {
         "workload": f"{cfg.name}: batch {cfg.batch} x {cfg.q_heads}q/{cfg.kv_heads}kv heads x head_dim {cfg.head_dim}, "
@@ -228,6 +292,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="cfg1", choices=sorted(synth.CONFIGS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--seq-sharded", action="store_true",
+                    help="also time configuration 3 (1M-token sequence sharded by rows over the ranks) and report "
+                         "it under the key seq_sharded_cfg3")
     ap.add_argument("--profile", action="store_true",
                     help="only the device-resident loop (for profiler captures): no e2e leg, no CPU baseline, "
                          "no clock sampling, warm-up taken as given")
@@ -353,8 +420,17 @@ def main():
         if world == 1 and not args.no_cpu_baseline:
             base, _ = cpu_reference_step_rate(cfg, host["k"], host["v"], q, budget_s=15.0, max_steps=20, sample_batch=2)
             line["cpu_baseline"] = base
-        print(json.dumps(line), flush=True)
+    else:
+        line = None
     eng.close()
+    del host, eng, res_k, res_v
+    torch.cuda.empty_cache()
+    if args.seq_sharded:
+        seq = run_seq_sharded(synth.CONFIGS["cfg3"], world, rank, device, args.steps, args.warmup)
+        if rank == 0:
+            line["seq_sharded_cfg3"] = seq
+    if rank == 0:
+        print(json.dumps(line), flush=True)
     if world > 1:
         import torch.distributed as dist
 

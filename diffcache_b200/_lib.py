@@ -40,7 +40,7 @@ SIGNATURES = {
                                 _vp, _vp, _vp, _i64, _i64, _i32, _f32, _vp, _vp, _vp, _vp, _vp, _u64]),
     "dc_sparse_attend_noalloc": (_i32, [_vp, _vp, _i64, _i64, _i32, _i32, _i32, _i32, _i32, _vp, _vp, _i64, _i32, _i64,
                                         _vp, _vp, _vp, _vp, _i64, _i64, _i32, _f32, _vp, _vp, _vp, _vp, _u64]),
-    "dc_lse_combine": (_i32, [_vp, _vp, _i32, _i64, _i32, _i32, _vp, _vp, _u64]),
+    "dc_lse_combine": (_i32, [_vp, _i64, _vp, _i64, _i32, _i64, _i32, _i32, _vp, _vp, _u64]),
     "dc_gather_rows": (_i32, [_vp, _i64, _i32, _i32, _vp, _i64, _i32, _vp, _u64]),
     "dc_pq_build_lut": (_i32, [_vp, _i32, _i32, _i32, _vp, _i32, _i32, _i32, _vp, _u64]),
     "dc_pq_adc_scan": (_i32, [_vp, _i64, _i32, _i64, _i32, _vp, _vp, _i64, _vp, _u64]),

@@ -252,23 +252,18 @@ sparse_attend_kernel(const AttendArgs a) {
     }
 }
 
-// Merge partials.  part_acc (rows, n_part, D) / part_ml (rows, n_part, 2) when part_major == 0
-// (the split-K layout above), or (n_part, rows, D) / (n_part, rows, 2) when part_major == 1 (the
-// layout an all-gather of per-rank partials produces).  Writes either the normalised output in
-// the element type (+ optional natural-log LSE) or the merged un-normalised (acc, m, l).
+// Merge partials: part s of row r is acc[s*acc_ps + r*acc_rs .. +dim), (m, l) at ml[s*ml_ps + r*ml_rs].
+// Split-K layout (rows, n_part, D): acc_ps = D, acc_rs = n_part*D.  All-gather layout
+// (n_part, rows, D): acc_ps = part stride, acc_rs = D.  Writes either the normalised output in the
+// element type (+ optional natural-log LSE) or the merged un-normalised (acc, m, l).
 template <int DT>
-__global__ void lse_combine_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml, int n_part,
-                                   int64_t rows, int dim, int part_major, uint16_t* __restrict__ out,
-                                   float* __restrict__ out_lse, float* __restrict__ out_acc,
-                                   float* __restrict__ out_ml) {
+__global__ void lse_combine_kernel(const float* __restrict__ part_acc, int64_t acc_ps, int64_t acc_rs,
+                                   const float* __restrict__ part_ml, int64_t ml_ps, int64_t ml_rs, int n_part,
+                                   int dim, uint16_t* __restrict__ out, float* __restrict__ out_lse,
+                                   float* __restrict__ out_acc, float* __restrict__ out_ml) {
     const int64_t row = blockIdx.x;
-    auto ml_at = [&](int s) {
-        return part_major ? part_ml + (static_cast<int64_t>(s) * rows + row) * 2 : part_ml + (row * n_part + s) * 2;
-    };
-    auto acc_at = [&](int s) {
-        return part_major ? part_acc + (static_cast<int64_t>(s) * rows + row) * dim
-                          : part_acc + (row * n_part + s) * dim;
-    };
+    auto ml_at = [&](int s) { return part_ml + s * ml_ps + row * ml_rs; };
+    auto acc_at = [&](int s) { return part_acc + s * acc_ps + row * acc_rs; };
     float m = -INFINITY;
     for (int s = 0; s < n_part; s++) m = fmaxf(m, ml_at(s)[0]);
     float l = 0.0f;
@@ -323,18 +318,21 @@ int64_t attend_scratch_bytes(int n_prob, int group, int head_dim) {
     return ctas * group * (head_dim + 2) * static_cast<int64_t>(sizeof(float));
 }
 
-int lse_combine(const float* acc, const float* ml, int n_part, int64_t rows, int head_dim, int dtype, int part_major,
-                void* out, float* out_lse, float* out_acc, float* out_ml, cudaStream_t stream) {
+int lse_combine(const float* acc, int64_t acc_ps, int64_t acc_rs, const float* ml, int64_t ml_ps, int64_t ml_rs,
+                int n_part, int64_t rows, int head_dim, int dtype, void* out, float* out_lse, float* out_acc,
+                float* out_ml, cudaStream_t stream) {
     DC_REQUIRE(acc && ml && n_part >= 1 && rows >= 0, "lse_combine: bad arguments");
     DC_REQUIRE(dtype == DC_BF16 || dtype == DC_FP16, "lse_combine: dtype %d not supported", dtype);
     if (rows == 0) return DC_OK;
     int threads = std::min(256, ((head_dim + 31) / 32) * 32);
     if (dtype == DC_BF16)
         lse_combine_kernel<DC_BF16><<<static_cast<unsigned>(rows), threads, 0, stream>>>(
-            acc, ml, n_part, rows, head_dim, part_major, static_cast<uint16_t*>(out), out_lse, out_acc, out_ml);
+            acc, acc_ps, acc_rs, ml, ml_ps, ml_rs, n_part, head_dim, static_cast<uint16_t*>(out), out_lse, out_acc,
+            out_ml);
     else
         lse_combine_kernel<DC_FP16><<<static_cast<unsigned>(rows), threads, 0, stream>>>(
-            acc, ml, n_part, rows, head_dim, part_major, static_cast<uint16_t*>(out), out_lse, out_acc, out_ml);
+            acc, acc_ps, acc_rs, ml, ml_ps, ml_rs, n_part, head_dim, static_cast<uint16_t*>(out), out_lse, out_acc,
+            out_ml);
     DC_CUDA_TRY(cudaGetLastError());
     return DC_OK;
 }
@@ -404,8 +402,9 @@ int sparse_attend(const void* k_store, const void* v_store, int64_t prob_stride,
     }
 #undef DC_ATT_CASE
     if (rc != DC_OK) return rc;
-    return lse_combine(a.part_acc, a.part_ml, a.n_split, static_cast<int64_t>(n_prob) * group, head_dim, dtype, 0, out,
-                       out_lse, out_acc, out_ml, stream);
+    return lse_combine(a.part_acc, head_dim, static_cast<int64_t>(a.n_split) * head_dim, a.part_ml, 2,
+                       static_cast<int64_t>(a.n_split) * 2, a.n_split, static_cast<int64_t>(n_prob) * group, head_dim,
+                       dtype, out, out_lse, out_acc, out_ml, stream);
 }
 
 }  // namespace dc

@@ -29,8 +29,9 @@ int sparse_attend(const void* k_store, const void* v_store, int64_t prob_stride,
                   void* res_v, int64_t res_stride_b, int64_t res_stride_h, int res_len, float scale, void* out,
                   float* out_lse, float* out_acc, float* out_ml, void* scratch, cudaStream_t stream);
 int64_t attend_scratch_bytes(int n_prob, int group, int head_dim);
-int lse_combine(const float* acc, const float* ml, int n_part, int64_t rows, int head_dim, int dtype, int part_major,
-                void* out, float* out_lse, float* out_acc, float* out_ml, cudaStream_t stream);
+int lse_combine(const float* acc, int64_t acc_ps, int64_t acc_rs, const float* ml, int64_t ml_ps, int64_t ml_rs,
+                int n_part, int64_t rows, int head_dim, int dtype, void* out, float* out_lse, float* out_acc,
+                float* out_ml, cudaStream_t stream);
 int pq_build_lut(const void* q, int q_mode, int group, int dtype, const float* centroids, int n_prob, int head_dim,
                  int n_sub, float* lut, cudaStream_t stream);
 int pq_adc_scan(const uint8_t* codes, int64_t prob_stride, int n_prob, int64_t n, int n_sub, const float* lut,
@@ -583,10 +584,12 @@ int dc_sparse_attend(const void* k_store, const void* v_store, int64_t prob_stri
                          scale, out, out_lse, out_acc, out_ml, scratch, as_stream(stream));
 }
 
-int dc_lse_combine(const float* acc, const float* ml, int n_part, int64_t rows, int head_dim, int dtype, void* out,
-                   float* out_lse, uint64_t stream) {
+int dc_lse_combine(const float* acc, int64_t acc_part_stride, const float* ml, int64_t ml_part_stride, int n_part,
+                   int64_t rows, int head_dim, int dtype, void* out, float* out_lse, uint64_t stream) {
     DC_REQUIRE(out != nullptr, "dc_lse_combine: null out");
-    return lse_combine(acc, ml, n_part, rows, head_dim, dtype, 1, out, out_lse, nullptr, nullptr, as_stream(stream));
+    DC_REQUIRE(acc_part_stride >= rows * head_dim && ml_part_stride >= rows * 2, "dc_lse_combine: part strides too small");
+    return lse_combine(acc, acc_part_stride, head_dim, ml, ml_part_stride, 2, n_part, rows, head_dim, dtype, out,
+                       out_lse, nullptr, nullptr, as_stream(stream));
 }
 
 int dc_gather_rows(const void* store, int64_t prob_stride, int n_prob, int head_dim, const uint32_t* ids,

@@ -1,0 +1,147 @@
+"""Multi-GPU decode steps: one process per GPU, ``torch.distributed`` for the plumbing.
+
+The reference is single-process and single-GPU (src/diffcache/base.py:28); it scales context by
+offloading to host memory.  On an 8-GPU box the same step shards instead:
+
+* :class:`SequenceShardedStep` — one very long sequence (1M tokens): the retrieval region is cut
+  into contiguous row ranges, one per rank.  Per step every rank scans its rows and selects a
+  local top-k; the ``(dist bits, global row id)`` candidates are all-gathered (k*8 bytes per
+  kv head and rank) and every rank runs the identical merge select, so all ranks agree on the
+  global top-k (same total order, ties to the smaller global id); each rank then attends over the
+  selected rows it owns (rank 0 adds the sink rows, the last rank the local window and the new
+  token) and the un-normalised partial results ``(acc, max, sum)`` are all-gathered and merged by
+  log-sum-exp.  No K/V row ever crosses NVLink.
+* :func:`shard_rows` / :func:`shard_heads` — the partition arithmetic, shared with the tests.
+
+The numerical work is delegated to a *backend* object so that the host logic (partitioning,
+gather layouts, offsets) can be exercised on CPU ranks over gloo with a stand-in backend;
+:class:`GpuShardBackend` is the real one (CUDA kernels through the C ABI).
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+from . import _lib
+
+PAD = 0xFFFFFFFF
+
+
+def shard_rows(n_rows: int, world: int) -> List[Tuple[int, int]]:
+    """Contiguous (start, length) row ranges, lengths differing by at most one 16-row block so
+    that every shard start stays aligned; covers [0, n_rows) exactly."""
+    block = 16
+    blocks = (n_rows + block - 1) // block
+    out, start = [], 0
+    for r in range(world):
+        nb = blocks // world + (1 if r < blocks % world else 0)
+        length = max(0, min(n_rows - start, nb * block))
+        out.append((start, length))
+        start += length
+    assert start == n_rows
+    return out
+
+
+def shard_heads(kv_heads: int, world: int) -> List[Tuple[int, int]]:
+    """KV-head sharding (one layer stack replicated over ranks, each owning a head range)."""
+    if kv_heads % world != 0:
+        raise ValueError(f"kv_heads={kv_heads} is not divisible by world={world}")
+    per = kv_heads // world
+    return [(r * per, per) for r in range(world)]
+
+
+class SequenceShardedStep:
+    """Sequence-sharded fused decode step.  ``backend`` provides
+
+    ``local_topk(q, k) -> (bits, gidx)``  int32/uint32-pattern tensors ``(P, k)``, padded with 0xFFFFFFFF
+    ``merge(bits_all, gidx_all, k) -> sel``  ``(P, k)`` global row ids from ``(P, world*k)`` candidates
+    ``attend_owned(q, sel) -> (acc, ml)``  fp32 ``(P*G, D)`` and ``(P*G, 2)``
+    ``combine(acc_all, ml_all) -> out``  from ``(world, P*G, D)`` / ``(world, P*G, 2)``
+    """
+
+    def __init__(self, backend, topk: int, group: Optional["dist.ProcessGroup"] = None):
+        self.backend = backend
+        self.topk = topk
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+
+    def _all_gather(self, t: torch.Tensor) -> torch.Tensor:
+        if self.world == 1:
+            return t.unsqueeze(0)
+        flat = t.contiguous().view(-1)
+        out = torch.empty(self.world * flat.numel(), dtype=t.dtype, device=t.device)
+        dist.all_gather_into_tensor(out, flat, group=self.group)
+        return out.view((self.world,) + tuple(t.shape))
+
+    def step(self, q: torch.Tensor) -> torch.Tensor:
+        k = self.topk
+        bits, gidx = self.backend.local_topk(q, k)                       # (P, k) each
+        cand = self._all_gather(torch.stack([bits, gidx]))               # (world, 2, P, k)
+        P = bits.shape[0]
+        cand = cand.permute(1, 2, 0, 3).reshape(2, P, self.world * k).contiguous()
+        sel = self.backend.merge(cand[0], cand[1], k)                    # (P, k) global ids, identical on all ranks
+        acc, ml = self.backend.attend_owned(q, sel)
+        acc_all = self._all_gather(acc)                                  # (world, P*G, D)
+        ml_all = self._all_gather(ml)                                    # (world, P*G, 2)
+        self.last_selection = sel
+        return self.backend.combine(acc_all, ml_all)
+
+
+class GpuShardBackend:
+    """One rank's share of a sequence-sharded step on its GPU (kernels through the C ABI)."""
+
+    def __init__(self, engine, row_offset: int, res_k=None, res_v=None, res_len: int = 0, k_new=None, v_new=None,
+                 scale: float = 0.0):
+        self.e = engine
+        self.e.set_row_offset(row_offset)
+        self.res_k, self.res_v, self.res_len = res_k, res_v, res_len
+        self.k_new, self.v_new = k_new, v_new
+        self.scale = scale
+        self.lib = _lib.load()
+        self.P = engine.bsz * engine.kv_head_num
+        self.G = engine.group
+        self.D = engine.head_dim
+        dev = torch.device("cuda", engine.device)
+        self.dev = dev
+        self._bufs = {}
+        self.status = torch.zeros(int(self.lib.dc_select_scratch_bytes(self.P)), dtype=torch.uint8, device=dev)
+
+    def _buf(self, name, shape, dtype):
+        key = (name, tuple(shape), dtype)
+        if key not in self._bufs:
+            self._bufs[key] = torch.empty(shape, dtype=dtype, device=self.dev)
+        return self._bufs[key]
+
+    @staticmethod
+    def _stream() -> int:
+        return int(torch.cuda.current_stream().cuda_stream)
+
+    def local_topk(self, q, k):
+        bits = self._buf("bits", (self.P, k), torch.int32)
+        gidx = self._buf("gidx", (self.P, k), torch.int32)
+        self.e.local_topk(q, k, bits, gidx)
+        return bits, gidx
+
+    def merge(self, bits_all, gidx_all, k):
+        n = bits_all.shape[1]
+        sel = self._buf("sel", (self.P, k), torch.int32)
+        _lib.check(self.lib.dc_topk_select(bits_all.data_ptr(), gidx_all.data_ptr(), n, self.P, n, k, None, None,
+                                           sel.data_ptr(), k, self.status.data_ptr(), self._stream()))
+        return sel
+
+    def attend_owned(self, q, sel):
+        acc = self._buf("acc", (self.P * self.G, self.D), torch.float32)
+        ml = self._buf("ml", (self.P * self.G, 2), torch.float32)
+        self.e.attend_owned(q, sel, sel.shape[1], acc, ml, res_k=self.res_k, res_v=self.res_v, res_len=self.res_len,
+                            k_new=self.k_new, v_new=self.v_new, scale=self.scale)
+        return acc, ml
+
+    def combine(self, acc_all, ml_all):
+        world, rows, D = acc_all.shape
+        out = self._buf("out", (self.e.bsz, self.e.q_head_num, D), torch.bfloat16 if self.e.dtype == 0 else torch.float16)
+        _lib.check(self.lib.dc_lse_combine(acc_all.data_ptr(), rows * D, ml_all.data_ptr(), rows * 2, world, rows, D,
+                                           self.e.dtype, out.data_ptr(), None, self._stream()))
+        return out

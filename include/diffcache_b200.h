@@ -295,12 +295,17 @@ int dc_sparse_attend_noalloc(const void* k_store, const void* v_store, int64_t p
                              void* out, float* out_lse, float* out_acc, float* out_ml, uint64_t stream);
 
 /*
- * Log-sum-exp merge of `n_part` partial results laid out as
- * acc (n_part, rows, head_dim) fp32 and ml (n_part, rows, 2) fp32 into
- * out (rows, head_dim) in the element type and optional lse (rows) fp32.
+ * Log-sum-exp merge of `n_part` partial results (split-K partials of one GPU, or
+ * the per-rank partials an all-gather delivers): part i holds
+ * acc_i = acc + i*acc_part_stride, (rows, head_dim) fp32, and
+ * ml_i = ml + i*ml_part_stride, (rows, 2) fp32 = (max in log2 units, sum); strides
+ * in floats.  Writes out (rows, head_dim) in the element type and optional
+ * lse (rows) fp32.  No counterpart in the reference (flash-attn merges its own
+ * splits internally, src/diffcache/base.py:134-142).
  */
-int dc_lse_combine(const float* acc, const float* ml, int n_part, int64_t rows, int head_dim,
-                   int dtype, void* out, float* out_lse, uint64_t stream);
+int dc_lse_combine(const float* acc, int64_t acc_part_stride, const float* ml, int64_t ml_part_stride,
+                   int n_part, int64_t rows, int head_dim, int dtype, void* out, float* out_lse,
+                   uint64_t stream);
 
 /* Gather rows: out[p][i][:] = store[p][ids[p][i]][:]  (nsw.rs:623-629). */
 int dc_gather_rows(const void* store, int64_t prob_stride, int n_prob, int head_dim,

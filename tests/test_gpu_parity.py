@@ -323,7 +323,8 @@ def test_sparse_attend_fp32_partials(lib, oracle_lib, G, D, n_sel):
     out = torch.zeros((P * G, D), dtype=torch.bfloat16, device="cuda")
     acc2 = torch.stack([acc, acc * 0, acc]).contiguous()
     ml2 = torch.stack([ml, torch.tensor([float("-inf"), 0.0], device="cuda").expand_as(ml), ml]).contiguous()
-    assert lib.dc_lse_combine(acc2.data_ptr(), ml2.data_ptr(), 3, P * G, D, 0, out.data_ptr(), None, _stream()) == 0
+    assert lib.dc_lse_combine(acc2.data_ptr(), P * G * D, ml2.data_ptr(), P * G * 2, 3, P * G, D, 0, out.data_ptr(), None,
+                              _stream()) == 0
     torch.cuda.synchronize()
     util.assert_attention_close(util.u16(out), of, 0, oracle_lib, ATOL, RTOL)
 
@@ -410,6 +411,60 @@ def test_kvcache_manager_flow(oracle_lib):
         else:  # an ulp tie at the boundary: the fused path must still agree with the three-call path
             assert sum(same) >= P - 1
     assert cache.kvbuf_suffix_len == suffix + 1
+
+
+def test_sequence_sharded_step_emulated_on_one_gpu(oracle_lib):
+    """The sequence-sharded step with every rank's engine on this one GPU and the two all-gathers
+    done by hand: local top-k with global ids and padding, merge select, attention over owned rows,
+    log-sum-exp merge — against the unsharded oracle step."""
+    from diffcache_b200 import DiffCacheGPU, sharded
+
+    B, Hkv, G, D, n_r, sink, win, topk, world = 1, 2, 4, 128, 5000, 16, 24, 1800, 3
+    P = B * Hkv
+    k, v, q = util.small_problem(B, Hkv, G, sink + n_r + win, D, seed=95)
+    qd = q.cuda()
+    parts = sharded.shard_rows(n_r, world)
+    backends, engines = [], []
+    for r, (start, length) in enumerate(parts):
+        eng = DiffCacheGPU(B, Hkv * G, Hkv, D, max_ctx_len=length)
+        eng.prefill(k[:, :, sink + start:sink + start + length].contiguous().cuda().view(torch.uint16),
+                    v[:, :, sink + start:sink + start + length].contiguous().cuda().view(torch.uint16))
+        res_k = res_v = kn = vn = None
+        rows = 0
+        if r == 0 or r == world - 1:
+            lo, hi = (0, sink) if r == 0 else (sink + n_r, sink + n_r + win - 1)
+            rows = hi - lo
+            res_k = torch.zeros((B, Hkv, rows + 2, D), dtype=torch.bfloat16, device="cuda")
+            res_v = torch.zeros_like(res_k)
+            res_k[:, :, :rows] = k[:, :, lo:hi].cuda(); res_v[:, :, :rows] = v[:, :, lo:hi].cuda()
+            if r == world - 1:
+                kn, vn = k[:, :, -1].contiguous().cuda(), v[:, :, -1].contiguous().cuda()
+        engines.append(eng)
+        backends.append(sharded.GpuShardBackend(eng, start, res_k, res_v, rows, kn, vn))
+    # what SequenceShardedStep.step does, with the gathers done by concatenation
+    cands = [torch.stack([t.clone() for t in b.local_topk(qd, topk)]) for b in backends]      # world x (2, P, k)
+    cand = torch.stack(cands).permute(1, 2, 0, 3).reshape(2, P, world * topk).contiguous()
+    sels = [b.merge(cand[0], cand[1], topk).clone() for b in backends]
+    assert all(torch.equal(sels[0], s) for s in sels)
+    parts_out = [tuple(t.clone() for t in b.attend_owned(qd, sels[0])) for b in backends]
+    out = backends[0].combine(torch.stack([a for a, _ in parts_out]).contiguous(),
+                              torch.stack([m for _, m in parts_out]).contiguous())
+    for e in engines:
+        e.check_status()
+    torch.cuda.synchronize()
+    ku, vu = util.u16(k).reshape(P, -1, D), util.u16(v).reshape(P, -1, D)
+    ref = util.oracle_decode_step(
+        oracle_lib, np.ascontiguousarray(ku[:, sink:sink + n_r]), np.ascontiguousarray(vu[:, sink:sink + n_r]),
+        util.u16(q).reshape(P * G, D), G, topk,
+        np.ascontiguousarray(np.concatenate([ku[:, :sink], ku[:, sink + n_r:-1]], 1)),
+        np.ascontiguousarray(np.concatenate([vu[:, :sink], vu[:, sink + n_r:-1]], 1)),
+        np.ascontiguousarray(ku[:, -1]), np.ascontiguousarray(vu[:, -1]), D ** -0.5, 0)
+    gi = sels[0].cpu().numpy().view(np.uint32)
+    subs = sum(util.check_selection_parity(gi[p], ref["idx"][p], ref["all_bits"][p]) for p in range(P))
+    if subs == 0:
+        util.assert_attention_close(util.u16(out).reshape(P * G, D), ref["out_f32"], 0, oracle_lib, ATOL, RTOL)
+    for e in engines:
+        e.close()
 
 
 def test_snapshot_roundtrip(tmp_path, oracle_lib):

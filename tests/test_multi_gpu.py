@@ -1,0 +1,81 @@
+"""Two real GPUs, NCCL: the sequence-sharded step of diffcache_b200.sharded against the single-GPU
+fused step on the same data.  Skipped on boxes with fewer than two GPUs."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _rank_main(rank, world, port, tmpdir):
+    import torch.distributed as dist
+
+    from diffcache_b200 import DiffCacheGPU, sharded, synth
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        B, Hkv, G, D, n_r, sink, win, topk = 1, 4, 4, 128, 40000, 64, 128, 2048
+        k, v = synth.make_kv(B, Hkv, sink + n_r + win, D, seed=5, dtype="bf16")
+        q = synth.make_query(k[:, :, sink:sink + n_r], G, seed=5).cuda()
+        start, length = sharded.shard_rows(n_r, world)[rank]
+        eng = DiffCacheGPU(B, Hkv * G, Hkv, D, max_ctx_len=length, device=rank)
+        eng.prefill(k[:, :, sink + start:sink + start + length].contiguous().cuda().view(torch.uint16),
+                    v[:, :, sink + start:sink + start + length].contiguous().cuda().view(torch.uint16))
+        res_k = res_v = kn = vn = None
+        rows = 0
+        if rank == 0 or rank == world - 1:
+            lo, hi = (0, sink) if rank == 0 else (sink + n_r, sink + n_r + win - 1)
+            rows = hi - lo
+            res_k = torch.zeros((B, Hkv, rows + 2, D), dtype=torch.bfloat16, device="cuda")
+            res_v = torch.zeros_like(res_k)
+            res_k[:, :, :rows] = k[:, :, lo:hi].cuda(); res_v[:, :, :rows] = v[:, :, lo:hi].cuda()
+            if rank == world - 1:
+                kn, vn = k[:, :, -1].contiguous().cuda(), v[:, :, -1].contiguous().cuda()
+        step = sharded.SequenceShardedStep(sharded.GpuShardBackend(eng, start, res_k, res_v, rows, kn, vn), topk)
+        out = step.step(q).clone()
+        sel = step.last_selection.clone()
+        eng.check_status()
+        torch.cuda.synchronize()
+        if rank == 0:  # single-GPU fused step on the whole sequence
+            full = DiffCacheGPU(B, Hkv * G, Hkv, D, max_ctx_len=n_r, device=0)
+            full.prefill(k[:, :, sink:sink + n_r].contiguous().cuda().view(torch.uint16),
+                         v[:, :, sink:sink + n_r].contiguous().cuda().view(torch.uint16))
+            rk = torch.zeros((B, Hkv, sink + win + 2, D), dtype=torch.bfloat16, device="cuda")
+            rv = torch.zeros_like(rk)
+            rk[:, :, :sink] = k[:, :, :sink].cuda(); rv[:, :, :sink] = v[:, :, :sink].cuda()
+            rk[:, :, sink:sink + win - 1] = k[:, :, sink + n_r:-1].cuda(); rv[:, :, sink:sink + win - 1] = v[:, :, sink + n_r:-1].cuda()
+            want = torch.empty_like(out)
+            idx = torch.zeros((B, Hkv, topk), dtype=torch.int32, device="cuda")
+            full.decode_attend(q, want, topk, res_k=rk, res_v=rv, res_len=sink + win - 1,
+                               k_new=k[:, :, -1].contiguous().cuda(), v_new=v[:, :, -1].contiguous().cuda(), out_idx=idx)
+            full.check_status()
+            torch.cuda.synchronize()
+            assert torch.equal(sel.view(B, Hkv, topk), idx), "sharded and single-GPU selections differ"
+            assert torch.allclose(out.float(), want.float(), rtol=2e-3, atol=1e-3)
+            full.close()
+        eng.close()
+        dist.barrier()
+        open(os.path.join(tmpdir, f"ok{rank}"), "w").write("ok")
+    finally:
+        dist.destroy_process_group()
+
+
+def test_sequence_sharded_step_on_two_gpus(tmp_path):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+
+    port = _free_port()
+    mp.spawn(_rank_main, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    assert (tmp_path / "ok0").exists() and (tmp_path / "ok1").exists()

@@ -30,6 +30,7 @@ constexpr int kSelThreads = 1024;
 constexpr int kBins = 4096;
 constexpr int kBinsLog2 = 12;
 constexpr int kCandCap = 2048;
+constexpr int kSegMax = 512;    // longest first-pass bin the in-place segment ordering accepts
 constexpr int kSelUnroll = 4;   // independent loads in flight per thread
 constexpr int kMaxPasses = 8;  // 64 key bits / 12 bits per pass = 6 passes at most
 
@@ -39,6 +40,7 @@ struct SelCtl {
     uint32_t t, below, cnt;
     uint32_t out_count, cand_count, dup_count;
     uint32_t mn, mx;
+    uint32_t max_seg;     // largest first-pass bin below the threshold bin
     uint32_t error;
 };
 
@@ -127,7 +129,7 @@ __device__ __forceinline__ void for_each_score(const uint32_t* __restrict__ pb, 
 }
 
 // grid = (cluster_size, n_prob), cluster = (cluster_size, 1, 1).
-// dynamic shared memory: out[kpad] u64 | cand[kCandCap] u64 | hist[kBins] u32
+// dynamic shared memory: out[kpad] u64 | cand[kCandCap] u64 | hist[kBins] u32 | cum[kBins] u32
 __global__ void __launch_bounds__(kSelThreads, 1)
 topk_select_kernel(const uint32_t* __restrict__ bits, const uint32_t* __restrict__ ids, int64_t in_stride, int64_t n,
                    int k, const uint32_t* __restrict__ minmax, uint32_t id_offset, uint32_t* __restrict__ out_bits,
@@ -142,6 +144,7 @@ topk_select_kernel(const uint32_t* __restrict__ bits, const uint32_t* __restrict
     unsigned long long* s_out = reinterpret_cast<unsigned long long*>(smem_raw);
     unsigned long long* s_cand = s_out + kpad;
     uint32_t* s_hist = reinterpret_cast<uint32_t*>(s_cand + kCandCap);
+    uint32_t* s_cum = s_hist + kBins;  // exclusive prefix of the first-pass histogram
     __shared__ SelCtl ctl;
     __shared__ uint32_t s_warp[32];
     __shared__ uint32_t s_total;
@@ -150,6 +153,7 @@ topk_select_kernel(const uint32_t* __restrict__ bits, const uint32_t* __restrict
     unsigned long long* l_out = cluster.map_shared_rank(s_out, 0);
     unsigned long long* l_cand = cluster.map_shared_rank(s_cand, 0);
     uint32_t* l_hist = cluster.map_shared_rank(s_hist, 0);
+    uint32_t* l_cum = cluster.map_shared_rank(s_cum, 0);
     SelCtl* l_ctl = cluster.map_shared_rank(&ctl, 0);
 
     const uint32_t* pb = bits + prob * in_stride;
@@ -165,11 +169,15 @@ topk_select_kernel(const uint32_t* __restrict__ bits, const uint32_t* __restrict
 
     if (tid == 0) {
         ctl.out_count = 0; ctl.cand_count = 0; ctl.dup_count = 0; ctl.error = 0;
-        ctl.mn = 0xFFFFFFFFu; ctl.mx = 0u;
+        ctl.mn = 0xFFFFFFFFu; ctl.mx = 0u; ctl.max_seg = 0;
     }
     __syncthreads();
 
     unsigned long long lo = 0, hi = ~0ull;
+    // first-pass binning (bits only): bin = (bits - bin_lo32) >> bin_sh; used again to place winners
+    uint32_t bin_lo32 = 0;
+    int bin_sh = 0, passes = 0;
+    bool first_bits_only = false;
     uint32_t need = static_cast<uint32_t>(k_eff);
     const bool take_all = (k_eff == n);
 
@@ -211,6 +219,7 @@ topk_select_kernel(const uint32_t* __restrict__ bits, const uint32_t* __restrict
             // the first pass): then this is pure 32-bit work and the ids are never read.
             const bool bits_only = (static_cast<uint32_t>(lo) == 0u) && (static_cast<uint32_t>(hi) == 0xFFFFFFFFu) &&
                                    shift >= 32;
+            if (pass == 0) { first_bits_only = bits_only; bin_lo32 = lo32; bin_sh = shift - 32; }
             if (bits_only) {
                 const uint32_t span = hi32 - lo32;
                 const int sh = shift - 32;
@@ -250,6 +259,23 @@ topk_select_kernel(const uint32_t* __restrict__ bits, const uint32_t* __restrict
                     }
                 }
                 if (tid == 0 && s_total < need) ctl.error = 1;  // cannot happen for consistent inputs
+                if (pass == 0) {
+                    // Keep where each bin starts in sorted order, note the largest bin that lies wholly
+                    // below the threshold, and recycle the histogram as per-bin fill counters.
+                    uint32_t run = ex;
+#pragma unroll
+                    for (int u = 0; u < 4; u++) { s_cum[tid * 4 + u] = run; run += h[u]; }
+                    __syncthreads();  // ctl.t visible
+                    const uint32_t tt = ctl.t;
+                    uint32_t mseg = 0;
+#pragma unroll
+                    for (int u = 0; u < 4; u++) {
+                        if (static_cast<uint32_t>(tid * 4 + u) < tt) mseg = max(mseg, h[u]);
+                        s_hist[tid * 4 + u] = 0;
+                    }
+                    mseg = __reduce_max_sync(0xFFFFFFFFu, mseg);
+                    if ((tid & 31) == 0 && mseg) atomicMax(&ctl.max_seg, mseg);
+                }
             }
             cluster.sync();  // ctl published
             const uint32_t t = l_ctl->t, below = l_ctl->below, cnt = l_ctl->cnt;
@@ -258,6 +284,7 @@ topk_select_kernel(const uint32_t* __restrict__ bits, const uint32_t* __restrict
             const unsigned long long span = shift == 0 ? 0ull : ((1ull << shift) - 1ull);
             const unsigned long long nhi = (nlo + span < nlo) ? hi : min(hi, nlo + span);
             lo = nlo; hi = nhi;
+            passes = pass + 1;
             if (cnt <= kCandCap || shift == 0) break;
         }
     }
@@ -266,6 +293,10 @@ topk_select_kernel(const uint32_t* __restrict__ bits, const uint32_t* __restrict
     cluster.sync();  // leader's counters are initialised / nobody still reads ctl.t
     const uint32_t base_out = static_cast<uint32_t>(k_eff) - need;  // keys strictly below lo
     const bool single_value = (lo == hi);
+    // One narrowing pass on the dist bits (the normal case): every winner below the threshold bin
+    // goes straight to its bin's segment of the sorted output, so only short segments remain to be
+    // ordered.  Otherwise winners are appended in arrival order and sorted afterwards.
+    const bool bucket = !take_all && passes == 1 && first_bits_only && l_ctl->max_seg <= kSegMax;
     if (take_all) {
         for_each_score(pb, begin, end, [&](uint32_t b, uint32_t i) {
             const uint32_t pos = warp_aggregated_inc(&l_ctl->out_count);
@@ -279,7 +310,13 @@ topk_select_kernel(const uint32_t* __restrict__ bits, const uint32_t* __restrict
             if (b > hi32) return;
             const unsigned long long key = key_of(b, i);
             if (key < lo) {
-                const uint32_t pos = warp_aggregated_inc(&l_ctl->out_count);
+                uint32_t pos;
+                if (bucket) {
+                    const uint32_t j = (b - bin_lo32) >> bin_sh;
+                    pos = l_cum[j] + atomicAdd(&l_hist[j], 1u);
+                } else {
+                    pos = warp_aggregated_inc(&l_ctl->out_count);
+                }
                 if (pos < static_cast<uint32_t>(kpad)) l_out[pos] = key;
             } else if (key <= hi) {
                 if (single_value) {
@@ -310,6 +347,32 @@ topk_select_kernel(const uint32_t* __restrict__ bits, const uint32_t* __restrict
         }
     }
     __syncthreads();
+    if (bucket) {
+        // The threshold-bin winners are already ordered at [base_out, k_eff).  Order the rest: the
+        // rank of a key inside its (short) segment is the number of smaller keys there, and the
+        // result is written straight to its final place in global memory.
+        const bool bad = ctl.error != 0;
+        if (bad && tid == 0 && status) atomicMax(status, 100u + ctl.error);
+        for (int p = tid; p < k; p += kSelThreads) {
+            unsigned long long key = ~0ull;
+            int target = p;
+            if (!bad && p < k_eff) {
+                key = s_out[p];
+                if (static_cast<uint32_t>(p) < base_out) {
+                    const uint32_t j = (static_cast<uint32_t>(key >> 32) - bin_lo32) >> bin_sh;
+                    const uint32_t seg = s_cum[j], cnt = s_hist[j];
+                    uint32_t rank = 0;
+                    for (uint32_t i = 0; i < cnt; i++) rank += (s_out[seg + i] < key) ? 1u : 0u;
+                    target = static_cast<int>(seg + rank);
+                }
+            }
+            const bool live = (!bad && p < k_eff);
+            if (out_bits) out_bits[prob * out_stride + target] = static_cast<uint32_t>(key >> 32);
+            if (out_ids)
+                out_ids[prob * out_stride + target] = static_cast<uint32_t>(key & 0xFFFFFFFFull) + (live ? id_offset : 0u);
+        }
+        return;
+    }
     if (!take_all && ctl.out_count != base_out && tid == 0) ctl.error = 3;
     for (int i = k_eff + tid; i < kpad; i += kSelThreads) s_out[i] = ~0ull;
     __syncthreads();
@@ -353,7 +416,7 @@ int topk_select(const uint32_t* bits, const uint32_t* ids, int64_t in_stride, in
     if (n_prob == 0 || k == 0) return DC_OK;
     int kpad = 1;
     while (kpad < k) kpad <<= 1;
-    size_t smem = static_cast<size_t>(kpad) * 8 + static_cast<size_t>(kCandCap) * 8 + kBins * 4;
+    size_t smem = static_cast<size_t>(kpad) * 8 + static_cast<size_t>(kCandCap) * 8 + 2 * kBins * 4;
 
     // Enough CTAs per problem to occupy the SMs, at most the portable cluster size of 8,
     // and no more than one CTA per 16K keys.

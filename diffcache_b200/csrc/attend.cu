@@ -20,7 +20,8 @@ namespace {
 
 constexpr int kAttThreads = 128;
 constexpr int kAttWarps = kAttThreads / 32;
-constexpr int kAttLoads = 8;  // rows per lane per tile
+constexpr int kAttLoads = 8;   // rows per lane per tile
+constexpr int kAttStages = 3;  // shared-memory ring depth (tiles)
 constexpr float kLog2e = 1.4426950408889634f;
 
 struct AttendArgs {
@@ -47,18 +48,35 @@ struct AttendArgs {
     float* part_ml;        // (n_prob, group, n_split, 2)
 };
 
+// 16-byte asynchronous global->shared copy (LDGSTS); src_bytes = 0 writes zeros instead.
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src, int src_bytes) {
+    const unsigned dst = static_cast<unsigned>(__cvta_generic_to_shared(smem_dst));
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(gmem_src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
+
 // grid = (n_split, n_prob, head_chunks); GC query heads of one kv head per CTA.
+//
+// The rows of a split are processed in tiles of TILE rows.  Tiles are staged through a ring of
+// kAttStages shared-memory buffers filled with asynchronous 16-byte copies issued kAttStages-1
+// tiles ahead, so the bytes in flight per SM are set by shared memory (two CTAs x two tiles x
+// TILE x 4*D bytes), not by registers; the row ids of the tile after that are fetched one
+// iteration earlier still, so a copy never waits for its address.
 template <int DT, int LPR, int GC>
 __global__ void __launch_bounds__(kAttThreads)
 sparse_attend_kernel(const AttendArgs a) {
     constexpr int D = LPR * 8;
-    constexpr int R = 32 / LPR;                 // rows per warp-wide load
+    constexpr int R = 32 / LPR;                 // rows per warp-wide access
     constexpr int WR = kAttLoads * R;           // rows per warp per tile
     constexpr int TILE = kAttWarps * WR;        // rows per CTA tile
     constexpr int NV = kAttLoads * GC;          // partial dot products per lane per tile
     constexpr int NRG = kAttWarps * R;          // row groups whose accumulators are merged at the end
     constexpr int CNT = treduce_count<NV, LPR>();
     constexpr int PLAIN = treduce_plain_bits<NV, LPR>();
+    constexpr int NS = kAttStages;
+    constexpr int STAGE_ELEMS = 2 * TILE * D;   // K tile then V tile
 
     const int tid = threadIdx.x;
     const int lane = tid & 31, warp = tid >> 5;
@@ -68,17 +86,19 @@ sparse_attend_kernel(const AttendArgs a) {
     const int g0 = blockIdx.z * GC;             // first query head of this chunk
     const int b = static_cast<int>(prob / a.kv_heads), h = static_cast<int>(prob % a.kv_heads);
 
-    __shared__ const uint16_t* s_kptr[TILE];
-    __shared__ const uint16_t* s_vptr[TILE];
+    extern __shared__ __align__(16) unsigned char att_smem[];
+    uint16_t* s_stage = reinterpret_cast<uint16_t*>(att_smem);                    // [NS][2][TILE][D]
+    float (*s_red)[GC][D + 4] = reinterpret_cast<float (*)[GC][D + 4]>(att_smem); // reuses the ring at the end
+    __shared__ unsigned char s_valid[NS][TILE];
     __shared__ float s_p[GC][TILE];
     __shared__ float s_alpha[GC], s_m[GC], s_l[GC];
-    __shared__ __align__(16) float s_red[NRG][GC][D + 4];  // written with 16-byte stores
 
     const int has_new = a.k_new != nullptr ? 1 : 0;
     const int total = a.n_sel + a.res_len + has_new;
     const int per = (total + a.n_split - 1) / a.n_split;
     const int j0 = min(total, split * per);
     const int j1 = min(total, j0 + per);
+    const int n_tiles = (j1 - j0 + TILE - 1) / TILE;
 
     // query heads of this chunk, pre-multiplied by scale*log2(e); heads beyond `group` are zero
     float qv[GC][8];
@@ -100,6 +120,7 @@ sparse_attend_kernel(const AttendArgs a) {
     const uint16_t* vst = a.v_store + prob * a.prob_stride;
     uint16_t* rk = a.res_k ? a.res_k + b * a.res_stride_b + h * a.res_stride_h : nullptr;
     uint16_t* rv = a.res_v ? a.res_v + b * a.res_stride_b + h * a.res_stride_h : nullptr;
+    const uint32_t* selp = a.sel ? a.sel + prob * a.sel_stride : nullptr;
 
     // flash-attn's in-place append of the new token (base.py:134-142): one CTA per problem
     if (has_new && split == 0 && blockIdx.z == 0 && rk != nullptr && tid < LPR) {
@@ -120,63 +141,89 @@ sparse_attend_kernel(const AttendArgs a) {
     const int base_idx = treduce_base<NV, LPR>(lane);
     const bool writer = (col & ((1 << PLAIN) - 1)) == 0;
 
-    for (int t0 = j0; t0 < j1; t0 += TILE) {
-        __syncthreads();  // previous tile fully consumed (s_p, pointers)
-        // ---- resolve the row list of this tile to addresses ----
-        for (int r = tid; r < TILE; r += kAttThreads) {
-            int j = t0 + r;
-            const uint16_t* kp = nullptr;
-            const uint16_t* vp = nullptr;
-            if (j < j1) {
-                if (j < a.n_sel) {
-                    int64_t row = static_cast<int64_t>(a.sel[prob * a.sel_stride + j]) - a.sel_base;
-                    if (row >= 0 && row < a.n_rows) { kp = kst + row * D; vp = vst + row * D; }
-                } else if (j < a.n_sel + a.res_len) {
-                    int64_t row = j - a.n_sel;
-                    kp = rk + row * D; vp = rv + row * D;
-                } else {
-                    kp = a.k_new + prob * D; vp = a.v_new + prob * D;
-                }
-            }
-            s_kptr[r] = kp; s_vptr[r] = vp;
-        }
-        __syncthreads();
-
-        // ---- K loads, partial dot products ----
-        const uint16_t* kptr[kAttLoads];
-        uint4 w[kAttLoads];
+    // Row ids of this lane's kAttLoads rows of tile `t` (0xFFFFFFFF where the slot is not a store row).
+    auto fetch_ids = [&](int t, uint32_t (&ids)[kAttLoads]) {
 #pragma unroll
         for (int i = 0; i < kAttLoads; i++) {
-            kptr[i] = s_kptr[warp * WR + i * R + sub];
-            w[i] = kptr[i] ? ld_stream16(kptr[i] + col * 8) : make_uint4(0, 0, 0, 0);
+            const int j = j0 + t * TILE + warp * WR + i * R + sub;
+            ids[i] = (t < n_tiles && j < j1 && j < a.n_sel) ? selp[j] : 0xFFFFFFFFu;
         }
+    };
+    // Issue the copies of tile `t` into its ring slot (one commit group per call, possibly empty).
+    auto issue_tile = [&](int t, const uint32_t (&ids)[kAttLoads]) {
+        if (t < n_tiles) {
+            uint16_t* ks = s_stage + (t % NS) * STAGE_ELEMS;
+            uint16_t* vs = ks + TILE * D;
+#pragma unroll
+            for (int i = 0; i < kAttLoads; i++) {
+                const int r = warp * WR + i * R + sub;
+                const int j = j0 + t * TILE + r;
+                const uint16_t* kp = nullptr;
+                const uint16_t* vp = nullptr;
+                if (j < j1) {
+                    if (j < a.n_sel) {
+                        const int64_t row = static_cast<int64_t>(ids[i]) - a.sel_base;
+                        if (row >= 0 && row < a.n_rows) { kp = kst + row * D; vp = vst + row * D; }
+                    } else if (j < a.n_sel + a.res_len) {
+                        const int64_t row = j - a.n_sel;
+                        kp = rk + row * D; vp = rv + row * D;
+                    } else {
+                        kp = a.k_new + prob * D; vp = a.v_new + prob * D;
+                    }
+                }
+                const bool ok = kp != nullptr;
+                // a skipped slot is zero-filled (src size 0) from any valid address
+                cp_async16(ks + r * D + col * 8, ok ? kp + col * 8 : a.q, ok ? 16 : 0);
+                cp_async16(vs + r * D + col * 8, ok ? vp + col * 8 : a.q, ok ? 16 : 0);
+                if (col == 0) s_valid[t % NS][r] = ok ? 1 : 0;
+            }
+        }
+        cp_async_commit();
+    };
+
+    uint32_t ids[kAttLoads];
+#pragma unroll
+    for (int t = 0; t < NS - 1; t++) {  // prologue: tiles 0 .. NS-2
+        fetch_ids(t, ids);
+        issue_tile(t, ids);
+    }
+    fetch_ids(NS - 1, ids);
+
+    for (int t = 0; t < n_tiles; t++) {
+        __syncthreads();  // tile t-1 fully consumed: its ring slot and s_p may be overwritten
+        issue_tile(t + NS - 1, ids);
+        fetch_ids(t + NS, ids);
+        cp_async_wait<NS - 1>();
+        __syncthreads();  // every thread's copies of tile t have landed
+
+        const uint16_t* ks = s_stage + (t % NS) * STAGE_ELEMS;
+        const uint16_t* vs = ks + TILE * D;
+        const unsigned char* valid = s_valid[t % NS];
+
+        // ---- Q.K partial dot products from shared memory ----
         float part[NV];
 #pragma unroll
         for (int i = 0; i < kAttLoads; i++) {
+            const int r = warp * WR + i * R + sub;
+            const uint4 w = *reinterpret_cast<const uint4*>(ks + r * D + col * 8);
             float f[8];
-            unpack8<DT>(w[i], f);
+            unpack8<DT>(w, f);
 #pragma unroll
             for (int g = 0; g < GC; g++) {
-                float s = f[0] * qv[g][0];
+                float sdot = f[0] * qv[g][0];
 #pragma unroll
-                for (int j = 1; j < 8; j++) s = fmaf(f[j], qv[g][j], s);
-                part[i * GC + g] = s;
+                for (int j = 1; j < 8; j++) sdot = fmaf(f[j], qv[g][j], sdot);
+                part[i * GC + g] = sdot;
             }
-        }
-        // ---- V loads go out now; their latency hides behind the reduction and softmax ----
-#pragma unroll
-        for (int i = 0; i < kAttLoads; i++) {
-            const uint16_t* vp = s_vptr[warp * WR + i * R + sub];
-            w[i] = vp ? ld_stream16(vp + col * 8) : make_uint4(0, 0, 0, 0);
         }
         treduce<NV, LPR>(part, lane);
         if (writer) {
 #pragma unroll
             for (int c = 0; c < CNT; c++) {
-                int idx = base_idx + c;       // = i * GC + g
-                int i = idx / GC, g = idx % GC;
-                int r = warp * WR + i * R + sub;
-                s_p[g][r] = s_kptr[r] ? part[c] : -INFINITY;
+                const int idx = base_idx + c;       // = i * GC + g
+                const int i = idx / GC, g = idx % GC;
+                const int r = warp * WR + i * R + sub;
+                s_p[g][r] = valid[r] ? part[c] : -INFINITY;
             }
         }
         __syncthreads();
@@ -192,8 +239,8 @@ sparse_attend_kernel(const AttendArgs a) {
             const float m_new = fmaxf(m_old, mx);
             float sum = 0.0f;
             for (int r = lane; r < TILE; r += 32) {
-                float s = s_p[g][r];
-                float p = (s == -INFINITY) ? 0.0f : exp2f(s - m_new);
+                float sc = s_p[g][r];
+                float p = (sc == -INFINITY) ? 0.0f : exp2f(sc - m_new);
                 s_p[g][r] = p;
                 sum += p;
             }
@@ -217,9 +264,10 @@ sparse_attend_kernel(const AttendArgs a) {
         }
 #pragma unroll
         for (int i = 0; i < kAttLoads; i++) {
-            float f[8];
-            unpack8<DT>(w[i], f);
             const int r = warp * WR + i * R + sub;
+            const uint4 w = *reinterpret_cast<const uint4*>(vs + r * D + col * 8);
+            float f[8];
+            unpack8<DT>(w, f);
 #pragma unroll
             for (int g = 0; g < GC; g++) {
                 float p = s_p[g][r];
@@ -228,6 +276,8 @@ sparse_attend_kernel(const AttendArgs a) {
             }
         }
     }
+    cp_async_wait<0>();
+    __syncthreads();  // the ring is idle: reuse it for the cross-row-group reduction
 
     // ---- merge the row groups' accumulators and write this split's partial ----
     const int rg = warp * R + sub;
@@ -286,28 +336,46 @@ __global__ void lse_combine_kernel(const float* __restrict__ part_acc, int64_t a
     }
 }
 
+constexpr size_t kAttSmemBytes = static_cast<size_t>(kAttStages) * 2 * (kAttWarps * kAttLoads * 4) * 64 * sizeof(uint16_t);
+// = stages x (K,V) x TILE x D x 2 bytes; TILE x D = 32 lanes-rows x 8 loads x 4 warps x 8 elements for every D
+
+template <int DT, int LPR, int GC>
+int launch_attend_gc(const AttendArgs& a, dim3 grid, cudaStream_t stream) {
+    // > 48 KB of dynamic shared memory needs an opt-in per kernel and device (not a stream operation)
+    static bool ready[64] = {};
+    int dev = 0;
+    DC_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64 || !ready[dev]) {
+        DC_CUDA_TRY(cudaFuncSetAttribute(sparse_attend_kernel<DT, LPR, GC>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(kAttSmemBytes)));
+        if (dev >= 0 && dev < 64) ready[dev] = true;
+    }
+    sparse_attend_kernel<DT, LPR, GC><<<grid, kAttThreads, kAttSmemBytes, stream>>>(a);
+    DC_CUDA_TRY(cudaGetLastError());
+    return DC_OK;
+}
+
 template <int DT, int LPR>
 int launch_attend(const AttendArgs& a, int n_prob, cudaStream_t stream) {
     int gc = a.group >= 3 ? 4 : a.group;
     int chunks = (a.group + gc - 1) / gc;
     dim3 grid(static_cast<unsigned>(a.n_split), static_cast<unsigned>(n_prob), static_cast<unsigned>(chunks));
-    if (gc == 1) sparse_attend_kernel<DT, LPR, 1><<<grid, kAttThreads, 0, stream>>>(a);
-    else if (gc == 2) sparse_attend_kernel<DT, LPR, 2><<<grid, kAttThreads, 0, stream>>>(a);
-    else sparse_attend_kernel<DT, LPR, 4><<<grid, kAttThreads, 0, stream>>>(a);
-    DC_CUDA_TRY(cudaGetLastError());
-    return DC_OK;
+    if (gc == 1) return launch_attend_gc<DT, LPR, 1>(a, grid, stream);
+    if (gc == 2) return launch_attend_gc<DT, LPR, 2>(a, grid, stream);
+    return launch_attend_gc<DT, LPR, 4>(a, grid, stream);
 }
 
 }  // namespace
 
 int attend_splits(int n_prob, int total_rows) {
-    // about kCtasPerSm CTAs per SM over the whole grid, at least 32 rows per split
+    // One wave: two CTAs fit on an SM (shared-memory ring), so split each problem's row list until
+    // the grid has about 2 x SMs CTAs, never more; at least 32 rows per split.
     static const int per_sm = [] {
         const char* s = std::getenv("DC_ATTEND_CTAS_PER_SM");
-        int v = (s && *s) ? std::atoi(s) : 4;
+        int v = (s && *s) ? std::atoi(s) : 2;
         return std::min(std::max(v, 1), 4);  // the scratch buffer is sized for at most 4 per SM
     }();
-    int target = (per_sm * sm_count() + n_prob - 1) / std::max(1, n_prob);
+    int target = std::max(1, (per_sm * sm_count()) / std::max(1, n_prob));
     int by_rows = std::max(1, (total_rows + 31) / 32);
     return std::max(1, std::min(std::min(target, by_rows), 256));
 }

@@ -1,0 +1,104 @@
+"""Full-depth decode step: a Llama-3-8B-shaped attention stack over per-layer retrieval engines.
+
+Every layer owns one ``DiffCacheGPU`` (as src/diffcache/kvcache/diffcache.py:87-100 owns one
+engine per layer).  A decode step runs, per layer: RMSNorm -> fused q/k/v projection -> the fused
+retrieval-attention step (scan, top-k, sparse attention incl. the new token) -> output projection
+-> residual.  The projections are plain ``torch.nn.functional.linear`` calls with random-init
+weights (they are not part of the retrieval path and the reference runs them through cuBLAS too,
+src/diffcache/llama.py:181-195); the MLP is left out: the configuration asks for the attention stack.
+
+With ``world > 1`` the stack is sharded by KV head: rank r owns kv heads
+``[r*Hkv/world, (r+1)*Hkv/world)`` of every layer, the matching query heads and the matching
+rows of the fused projection, so scan / select / attend are local; the per-layer exchange is one
+all-gather of the attention output slice ``(B, Hq/world * D)`` before a replicated output
+projection (deterministic: every rank computes the same residual stream).
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+import torch.nn.functional as F
+
+from . import synth
+from .engine import DiffCacheGPU
+from .sharded import shard_heads
+
+
+class AttentionStack:
+    def __init__(self, n_layers: int, hidden: int, batch: int, q_heads: int, kv_heads: int, head_dim: int,
+                 context: int, topk: int, sink: int, window: int, dtype: str = "bf16", seed: int = 2000,
+                 device: Optional[torch.device] = None, group: Optional["dist.ProcessGroup"] = None):
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.pg = group
+        self.device = device or torch.device("cuda", torch.cuda.current_device())
+        self.n_layers, self.hidden, self.batch = n_layers, hidden, batch
+        self.head_dim, self.topk = head_dim, topk
+        h0, self.kv_local = shard_heads(kv_heads, self.world)[self.rank]
+        g = q_heads // kv_heads
+        self.q_local = self.kv_local * g
+        self.q_heads, self.kv_heads = q_heads, kv_heads
+        dt = synth.torch_dtype(dtype)
+        n_r = context - sink - window
+        self.res_rows = sink + window - 1
+        self.engines, self.res_k, self.res_v, self.wqkv, self.wo, self.norm_w = [], [], [], [], [], []
+        for layer in range(n_layers):
+            wgen = torch.Generator(device=self.device).manual_seed(seed + 10 * layer + 5)
+            # fused projection rows for the local heads: [q_local*D | kv_local*D | kv_local*D]
+            full = torch.randn(((q_heads + 2 * kv_heads) * head_dim, hidden), generator=wgen, device=self.device) * 0.02
+            qs = full[h0 * g * head_dim:(h0 + self.kv_local) * g * head_dim]
+            ko = q_heads * head_dim
+            ks = full[ko + h0 * head_dim:ko + (h0 + self.kv_local) * head_dim]
+            vo = (q_heads + kv_heads) * head_dim
+            vs = full[vo + h0 * head_dim:vo + (h0 + self.kv_local) * head_dim]
+            self.wqkv.append(torch.cat([qs, ks, vs]).to(dt).contiguous())
+            self.wo.append((torch.randn((hidden, q_heads * head_dim), generator=wgen, device=self.device) * 0.02).to(dt))
+            self.norm_w.append(torch.ones(hidden, dtype=dt, device=self.device))
+            del full
+            # KV cache of this layer for the local heads, generated in place (same seed on every rank,
+            # then the local head slice is kept)
+            k, v = synth.make_kv(batch, kv_heads, context, head_dim, seed + layer, dtype, device=self.device)
+            k, v = k[:, h0:h0 + self.kv_local], v[:, h0:h0 + self.kv_local]
+            eng = DiffCacheGPU(batch, self.q_local, self.kv_local, head_dim, max_ctx_len=n_r, dtype=dtype,
+                               device=self.device.index, use_bruteforce=True, name=f"l{layer:03d}")
+            eng.prefill(k[:, :, sink:sink + n_r], v[:, :, sink:sink + n_r])
+            rk = torch.zeros((batch, self.kv_local, sink + window + 8, head_dim), dtype=dt, device=self.device)
+            rv = torch.zeros_like(rk)
+            for dst, src in ((rk, k), (rv, v)):
+                dst[:, :, :sink] = src[:, :, :sink]
+                dst[:, :, sink:self.res_rows] = src[:, :, sink + n_r:context - 1]
+            self.engines.append(eng)
+            self.res_k.append(rk)
+            self.res_v.append(rv)
+            del k, v
+        self.attn_local = torch.empty((batch, self.q_local, head_dim), dtype=dt, device=self.device)
+        self.attn_full = torch.empty((self.world, batch, self.q_local * head_dim), dtype=dt, device=self.device)
+        torch.cuda.synchronize(self.device)
+
+    def step(self, x: torch.Tensor) -> torch.Tensor:
+        """x ``(batch, hidden)`` -> ``(batch, hidden)`` after all layers.  The resident length is not
+        advanced, so repeated calls time the same step."""
+        B, D = self.batch, self.head_dim
+        nq, nkv = self.q_local * D, self.kv_local * D
+        for layer in range(self.n_layers):
+            h = F.rms_norm(x, (self.hidden,), self.norm_w[layer], 1e-5)
+            qkv = F.linear(h, self.wqkv[layer])
+            q = qkv[:, :nq].contiguous().view(B, self.q_local, D)
+            kn = qkv[:, nq:nq + nkv].contiguous().view(B, self.kv_local, D)
+            vn = qkv[:, nq + nkv:].contiguous().view(B, self.kv_local, D)
+            self.engines[layer].decode_attend(q, self.attn_local, self.topk, res_k=self.res_k[layer],
+                                              res_v=self.res_v[layer], res_len=self.res_rows, k_new=kn, v_new=vn)
+            if self.world > 1:
+                dist.all_gather_into_tensor(self.attn_full.view(-1), self.attn_local.view(-1), group=self.pg)
+                attn = self.attn_full.view(self.world, B, self.kv_local, -1).permute(1, 0, 2, 3).reshape(B, -1)
+            else:
+                attn = self.attn_local.view(B, -1)
+            x = x + F.linear(attn, self.wo[layer])
+        return x
+
+    def close(self) -> None:
+        for e in self.engines:
+            e.close()
+        self.engines = []

@@ -18,9 +18,9 @@ namespace dc {
 
 namespace {
 
-constexpr int kAttThreads = 128;
+constexpr int kAttThreads = 256;
 constexpr int kAttWarps = kAttThreads / 32;
-constexpr int kAttLoads = 8;   // rows per lane per tile
+constexpr int kAttLoads = 4;   // rows per lane per tile
 constexpr int kAttStages = 3;  // shared-memory ring depth (tiles)
 constexpr float kLog2e = 1.4426950408889634f;
 

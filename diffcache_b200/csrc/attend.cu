@@ -5,10 +5,10 @@
 // (src/diffcache/kvcache/diffcache.py:196-209) and flash_attn_with_kvcache over
 // [retrieved | prefix | suffix | new token] (src/diffcache/base.py:134-142).
 // The selected rows are read in place from the HBM store: every row is one contiguous
-// 2*head_dim-byte segment fetched with 16-byte loads by the lanes that share it, all
-// query heads of the kv head are served from the same read, and the row list of a problem
-// is split over several CTAs whose (max, sum, accumulator) partials are merged by
-// log-sum-exp in a second small kernel.
+// 2*head_dim-byte segment copied asynchronously (16 bytes per lane) into a shared-memory ring,
+// all query heads of the kv head are served from the same copy with tensor-core MMAs, and the
+// row list of a problem is split over several CTAs whose (max, sum, accumulator) partials are
+// merged by log-sum-exp in a second small kernel.
 #include <cmath>
 #include <cstdlib>
 
@@ -18,10 +18,8 @@ namespace dc {
 
 namespace {
 
-constexpr int kAttThreads = 256;
+constexpr int kAttThreads = 128;
 constexpr int kAttWarps = kAttThreads / 32;
-constexpr int kAttLoads = 4;   // rows per lane per tile
-constexpr int kAttStages = 3;  // shared-memory ring depth (tiles)
 constexpr float kLog2e = 1.4426950408889634f;
 
 struct AttendArgs {
@@ -57,41 +55,110 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
 
-// grid = (n_split, n_prob, head_chunks); GC query heads of one kv head per CTA.
+// ---- warp-level tensor-core primitives (m16n8k16, fp32 accumulate) ----
+// Only rows 0..7 of the 16-row A/C tiles are used (query heads of one kv head), so the A registers of
+// rows 8..15 are zero and the matching accumulator halves are discarded.
+template <int DT>
+__device__ __forceinline__ void mma_16816(float& d0, float& d1, uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+    float z2, z3;
+    if (DT == DC_BF16) {
+        asm volatile(
+            "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%10,%10};\n"
+            : "+f"(d0), "+f"(d1), "=f"(z2), "=f"(z3)
+            : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1), "f"(0.0f));
+    } else {
+        asm volatile(
+            "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%10,%10};\n"
+            : "+f"(d0), "+f"(d1), "=f"(z2), "=f"(z3)
+            : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1), "f"(0.0f));
+    }
+}
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* smem_row) {
+    const unsigned addr = static_cast<unsigned>(__cvta_generic_to_shared(smem_row));
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* smem_row) {
+    const unsigned addr = static_cast<unsigned>(__cvta_generic_to_shared(smem_row));
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+
+// Two fp32 values -> packed 16-bit pair (first value in the low half) plus the packed rounding
+// residue, so that hi + lo reproduces the fp32 values to ~2^-17 when both feed the MMA.
+template <int DT>
+__device__ __forceinline__ void pack_hi_lo(float x, float y, uint32_t& hi, uint32_t& lo) {
+    if (DT == DC_BF16) {
+        __nv_bfloat162 h = __floats2bfloat162_rn(x, y);
+        float2 hf = __bfloat1622float2(h);
+        __nv_bfloat162 l = __floats2bfloat162_rn(x - hf.x, y - hf.y);
+        hi = *reinterpret_cast<uint32_t*>(&h);
+        lo = *reinterpret_cast<uint32_t*>(&l);
+    } else {
+        __half2 h = __floats2half2_rn(x, y);
+        float2 hf = __half22float2(h);
+        __half2 l = __floats2half2_rn(x - hf.x, y - hf.y);
+        hi = *reinterpret_cast<uint32_t*>(&h);
+        lo = *reinterpret_cast<uint32_t*>(&l);
+    }
+}
+
+constexpr int kHeadsPerCta = 8;   // query heads of one kv head handled by one CTA (rows 0..7 of the MMA tile)
+
+// Per head_dim: rows per tile and ring depth.  A tile is kAttWarps x 16 x RB rows; every warp owns
+// 16*RB rows of it for BOTH Q.K^T and P.V (split-K across warps, merged once at the end), so the
+// main loop needs no block barrier except the hand-over of ring slots.
+template <int LPR> struct AttCfg;
+template <> struct AttCfg<8>  { static constexpr int RB = 2; static constexpr int NS = 3; };  // D = 64:  128-row tiles, 32 KB
+template <> struct AttCfg<16> { static constexpr int RB = 1; static constexpr int NS = 2; };  // D = 128:  64-row tiles, 32 KB
+template <> struct AttCfg<32> { static constexpr int RB = 1; static constexpr int NS = 3; };  // D = 256:  64-row tiles, 64 KB
+
+template <int LPR>
+constexpr size_t att_smem_bytes() {
+    return static_cast<size_t>(AttCfg<LPR>::NS) * 2 * (kAttWarps * 16 * AttCfg<LPR>::RB) * (LPR * 8) * sizeof(uint16_t);
+}
+
+// Byte offset of 16-byte chunk `chunk` of row `row` inside a [rows][D] tile: the chunk index is XORed
+// with the low row bits so that the 8 rows of an ldmatrix 8x8 block fall into 8 different bank groups.
+template <int D>
+__device__ __forceinline__ int swz(int row, int chunk) { return row * (D * 2) + ((chunk ^ (row & 7)) << 4); }
+
+// grid = (n_split, n_prob, ceil(group / 8)).
 //
-// The rows of a split are processed in tiles of TILE rows.  Tiles are staged through a ring of
-// kAttStages shared-memory buffers filled with asynchronous 16-byte copies issued kAttStages-1
-// tiles ahead, so the bytes in flight per SM are set by shared memory (two CTAs x two tiles x
-// TILE x 4*D bytes), not by registers; the row ids of the tile after that are fetched one
-// iteration earlier still, so a copy never waits for its address.
-template <int DT, int LPR, int GC>
+// The rows of a split are processed in tiles staged through a ring of shared-memory buffers filled
+// with asynchronous 16-byte copies issued NS-1 tiles ahead (row ids are fetched one iteration before
+// that), so bytes in flight are set by shared memory, not registers.  Q.K^T and P.V run on the tensor
+// cores: K rows are the "col-major" B operand of S = Q.K^T as they lie in memory, V rows become the B
+// operand of O = P.V through ldmatrix.trans, and the S accumulator fragments are re-used in place as
+// the A fragments of P (split into a 16-bit value and its rounding residue so that P keeps ~17 bits).
+template <int DT, int LPR>
 __global__ void __launch_bounds__(kAttThreads)
 sparse_attend_kernel(const AttendArgs a) {
     constexpr int D = LPR * 8;
-    constexpr int R = 32 / LPR;                 // rows per warp-wide access
-    constexpr int WR = kAttLoads * R;           // rows per warp per tile
-    constexpr int TILE = kAttWarps * WR;        // rows per CTA tile
-    constexpr int NV = kAttLoads * GC;          // partial dot products per lane per tile
-    constexpr int NRG = kAttWarps * R;          // row groups whose accumulators are merged at the end
-    constexpr int CNT = treduce_count<NV, LPR>();
-    constexpr int PLAIN = treduce_plain_bits<NV, LPR>();
-    constexpr int NS = kAttStages;
-    constexpr int STAGE_ELEMS = 2 * TILE * D;   // K tile then V tile
+    constexpr int RB = AttCfg<LPR>::RB;
+    constexpr int NS = AttCfg<LPR>::NS;
+    constexpr int RW = 16 * RB;                 // rows per warp per tile
+    constexpr int TILE = kAttWarps * RW;        // rows per CTA tile
+    constexpr int R = 32 / LPR;                 // rows covered by one warp-wide copy instruction
+    constexpr int NCOPY = RW / R;               // copy instructions per lane per tile and tensor
+    constexpr int STAGE_BYTES = 2 * TILE * D * 2;
+    constexpr int KSTEPS = D / 16;
+    constexpr int NT = D / 8;                   // 8-column output tiles
 
     const int tid = threadIdx.x;
     const int lane = tid & 31, warp = tid >> 5;
     const int col = lane % LPR, sub = lane / LPR;
+    const int gq = lane >> 2, tq = lane & 3;    // MMA fragment coordinates: row (head) and column pair
     const int64_t prob = blockIdx.y;
     const int split = blockIdx.x;
-    const int g0 = blockIdx.z * GC;             // first query head of this chunk
+    const int g0 = blockIdx.z * kHeadsPerCta;   // first query head of this chunk
+    const int n_heads = min(kHeadsPerCta, a.group - g0);
     const int b = static_cast<int>(prob / a.kv_heads), h = static_cast<int>(prob % a.kv_heads);
 
-    extern __shared__ __align__(16) unsigned char att_smem[];
-    uint16_t* s_stage = reinterpret_cast<uint16_t*>(att_smem);                    // [NS][2][TILE][D]
-    float (*s_red)[GC][D + 4] = reinterpret_cast<float (*)[GC][D + 4]>(att_smem); // reuses the ring at the end
+    extern __shared__ __align__(128) unsigned char att_smem[];
     __shared__ unsigned char s_valid[NS][TILE];
-    __shared__ float s_p[GC][TILE];
-    __shared__ float s_alpha[GC], s_m[GC], s_l[GC];
+    __shared__ float s_ml[kAttWarps][kHeadsPerCta][2];
 
     const int has_new = a.k_new != nullptr ? 1 : 0;
     const int total = a.n_sel + a.res_len + has_new;
@@ -100,19 +167,14 @@ sparse_attend_kernel(const AttendArgs a) {
     const int j1 = min(total, j0 + per);
     const int n_tiles = (j1 - j0 + TILE - 1) / TILE;
 
-    // query heads of this chunk, pre-multiplied by scale*log2(e); heads beyond `group` are zero
-    float qv[GC][8];
+    // A fragments of Q for every k-step: rows = heads of this chunk (zero beyond), raw 16-bit pairs
+    uint32_t qa[KSTEPS][2];
+    {
+        const uint16_t* qrow = a.q + (prob * a.group + g0 + gq) * D;
 #pragma unroll
-    for (int g = 0; g < GC; g++) {
-        if (g0 + g < a.group) {
-            uint4 w = *reinterpret_cast<const uint4*>(a.q + (prob * a.group + g0 + g) * D + col * 8);
-            float f[8];
-            unpack8<DT>(w, f);
-#pragma unroll
-            for (int j = 0; j < 8; j++) qv[g][j] = f[j] * a.scale_log2;
-        } else {
-#pragma unroll
-            for (int j = 0; j < 8; j++) qv[g][j] = 0.0f;
+        for (int ks = 0; ks < KSTEPS; ks++) {
+            qa[ks][0] = gq < n_heads ? *reinterpret_cast<const uint32_t*>(qrow + 16 * ks + 2 * tq) : 0u;
+            qa[ks][1] = gq < n_heads ? *reinterpret_cast<const uint32_t*>(qrow + 16 * ks + 2 * tq + 8) : 0u;
         }
     }
 
@@ -130,58 +192,85 @@ sparse_attend_kernel(const AttendArgs a) {
             reinterpret_cast<const uint4*>(a.v_new + prob * D)[tid];
     }
 
-    if (tid < GC) { s_m[tid] = -INFINITY; s_l[tid] = 0.0f; }
-
-    float acc[GC][8];
+    // Row ids of this lane's NCOPY rows of tile `t` (0xFFFFFFFF where the slot is not a store row).
+    auto fetch_ids = [&](int t, uint32_t (&ids)[NCOPY]) {
 #pragma unroll
-    for (int g = 0; g < GC; g++)
-#pragma unroll
-        for (int j = 0; j < 8; j++) acc[g][j] = 0.0f;
-
-    const int base_idx = treduce_base<NV, LPR>(lane);
-    const bool writer = (col & ((1 << PLAIN) - 1)) == 0;
-
-    // Row ids of this lane's kAttLoads rows of tile `t` (0xFFFFFFFF where the slot is not a store row).
-    auto fetch_ids = [&](int t, uint32_t (&ids)[kAttLoads]) {
-#pragma unroll
-        for (int i = 0; i < kAttLoads; i++) {
-            const int j = j0 + t * TILE + warp * WR + i * R + sub;
+        for (int i = 0; i < NCOPY; i++) {
+            const int j = j0 + t * TILE + warp * RW + i * R + sub;
             ids[i] = (t < n_tiles && j < j1 && j < a.n_sel) ? selp[j] : 0xFFFFFFFFu;
         }
     };
     // Issue the copies of tile `t` into its ring slot (one commit group per call, possibly empty).
-    auto issue_tile = [&](int t, const uint32_t (&ids)[kAttLoads]) {
-        if (t < n_tiles) {
-            uint16_t* ks = s_stage + (t % NS) * STAGE_ELEMS;
-            uint16_t* vs = ks + TILE * D;
+    // Fast path: every row of the tile is a selected store row, so a row address is one multiply-add
+    // from its id and the V address is the K address plus a constant.
+    int soff[NCOPY];  // swizzled byte offset of this lane's chunk of each of its rows inside a K (or V) tile
 #pragma unroll
-            for (int i = 0; i < kAttLoads; i++) {
-                const int r = warp * WR + i * R + sub;
-                const int j = j0 + t * TILE + r;
-                const uint16_t* kp = nullptr;
-                const uint16_t* vp = nullptr;
-                if (j < j1) {
-                    if (j < a.n_sel) {
-                        const int64_t row = static_cast<int64_t>(ids[i]) - a.sel_base;
-                        if (row >= 0 && row < a.n_rows) { kp = kst + row * D; vp = vst + row * D; }
-                    } else if (j < a.n_sel + a.res_len) {
-                        const int64_t row = j - a.n_sel;
-                        kp = rk + row * D; vp = rv + row * D;
-                    } else {
-                        kp = a.k_new + prob * D; vp = a.v_new + prob * D;
-                    }
+    for (int i = 0; i < NCOPY; i++) soff[i] = swz<D>(warp * RW + i * R + sub, col);
+    const uint16_t* kst_col = kst + col * 8;
+    const int64_t v_minus_k = vst - kst;  // elements
+    auto issue_tile = [&](int t, const uint32_t (&ids)[NCOPY]) {
+        if (t < n_tiles) {
+            unsigned char* ks = att_smem + (t % NS) * STAGE_BYTES;
+            unsigned char* vs = ks + TILE * D * 2;
+            const int jt = j0 + t * TILE;
+            if (jt + TILE <= min(j1, a.n_sel)) {
+#pragma unroll
+                for (int i = 0; i < NCOPY; i++) {
+                    const int64_t row = static_cast<int64_t>(ids[i]) - a.sel_base;
+                    const bool ok = row >= 0 && row < a.n_rows;  // ids of other shards and pads are skipped
+                    const uint16_t* kp = ok ? kst_col + row * D : a.q;
+                    cp_async16(ks + soff[i], kp, ok ? 16 : 0);
+                    cp_async16(vs + soff[i], ok ? kp + v_minus_k : a.q, ok ? 16 : 0);
+                    if (col == 0) s_valid[t % NS][warp * RW + i * R + sub] = ok ? 1 : 0;
                 }
-                const bool ok = kp != nullptr;
-                // a skipped slot is zero-filled (src size 0) from any valid address
-                cp_async16(ks + r * D + col * 8, ok ? kp + col * 8 : a.q, ok ? 16 : 0);
-                cp_async16(vs + r * D + col * 8, ok ? vp + col * 8 : a.q, ok ? 16 : 0);
-                if (col == 0) s_valid[t % NS][r] = ok ? 1 : 0;
+            } else if (jt >= a.n_sel && jt + TILE <= min(j1, a.n_sel + a.res_len)) {
+                // a tile of resident (sink / window) rows: consecutive rows of the caller's buffer
+                const uint16_t* kp0 = rk + static_cast<int64_t>(jt - a.n_sel + warp * RW + sub) * D + col * 8;
+                const int64_t rv_minus_rk = rv - rk;
+#pragma unroll
+                for (int i = 0; i < NCOPY; i++) {
+                    const uint16_t* kp = kp0 + i * R * D;
+                    cp_async16(ks + soff[i], kp, 16);
+                    cp_async16(vs + soff[i], kp + rv_minus_rk, 16);
+                    if (col == 0) s_valid[t % NS][warp * RW + i * R + sub] = 1;
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < NCOPY; i++) {
+                    const int r = warp * RW + i * R + sub;
+                    const int j = jt + r;
+                    const uint16_t* kp = nullptr;
+                    const uint16_t* vp = nullptr;
+                    if (j < j1) {
+                        if (j < a.n_sel) {
+                            const int64_t row = static_cast<int64_t>(ids[i]) - a.sel_base;
+                            if (row >= 0 && row < a.n_rows) { kp = kst + row * D; vp = vst + row * D; }
+                        } else if (j < a.n_sel + a.res_len) {
+                            const int64_t row = j - a.n_sel;
+                            kp = rk + row * D; vp = rv + row * D;
+                        } else {
+                            kp = a.k_new + prob * D; vp = a.v_new + prob * D;
+                        }
+                    }
+                    const bool ok = kp != nullptr;
+                    // a skipped slot is zero-filled (source size 0) from any valid address
+                    cp_async16(ks + soff[i], ok ? kp + col * 8 : a.q, ok ? 16 : 0);
+                    cp_async16(vs + soff[i], ok ? vp + col * 8 : a.q, ok ? 16 : 0);
+                    if (col == 0) s_valid[t % NS][r] = ok ? 1 : 0;
+                }
             }
         }
         cp_async_commit();
     };
 
-    uint32_t ids[kAttLoads];
+    // per-lane softmax state of head gq over this warp's rows (identical in the 4 lanes of a head,
+    // except l_run which is each lane's partial sum) and the output accumulators O[gq][8*nt + 2*tq, +1]
+    float m_run = -INFINITY, l_run = 0.0f;
+    float o_acc[NT][2];
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++) { o_acc[nt][0] = 0.0f; o_acc[nt][1] = 0.0f; }
+
+    uint32_t ids[NCOPY];
 #pragma unroll
     for (int t = 0; t < NS - 1; t++) {  // prologue: tiles 0 .. NS-2
         fetch_ids(t, ids);
@@ -190,115 +279,102 @@ sparse_attend_kernel(const AttendArgs a) {
     fetch_ids(NS - 1, ids);
 
     for (int t = 0; t < n_tiles; t++) {
-        __syncthreads();  // tile t-1 fully consumed: its ring slot and s_p may be overwritten
+        __syncthreads();  // tile t-1 fully consumed: its ring slot may be overwritten
         issue_tile(t + NS - 1, ids);
         fetch_ids(t + NS, ids);
         cp_async_wait<NS - 1>();
         __syncthreads();  // every thread's copies of tile t have landed
 
-        const uint16_t* ks = s_stage + (t % NS) * STAGE_ELEMS;
-        const uint16_t* vs = ks + TILE * D;
+        const unsigned char* ks = att_smem + (t % NS) * STAGE_BYTES;
+        const unsigned char* vs = ks + TILE * D * 2;
         const unsigned char* valid = s_valid[t % NS];
 
-        // ---- Q.K partial dot products from shared memory ----
-        float part[NV];
 #pragma unroll
-        for (int i = 0; i < kAttLoads; i++) {
-            const int r = warp * WR + i * R + sub;
-            const uint4 w = *reinterpret_cast<const uint4*>(ks + r * D + col * 8);
-            float f[8];
-            unpack8<DT>(w, f);
+        for (int rb = 0; rb < RB; rb++) {
+            const int row0 = warp * RW + rb * 16;  // this warp's 16 rows
+            // ---- S = Q.K^T for two 8-row groups: sc[2*grp + {0,1}] = rows row0 + 8*grp + 2*tq + {0,1} ----
+            float sc[4];
 #pragma unroll
-            for (int g = 0; g < GC; g++) {
-                float sdot = f[0] * qv[g][0];
+            for (int grp = 0; grp < 2; grp++) {
+                float c0 = 0.0f, c1 = 0.0f;
 #pragma unroll
-                for (int j = 1; j < 8; j++) sdot = fmaf(f[j], qv[g][j], sdot);
-                part[i * GC + g] = sdot;
+                for (int kk = 0; kk < KSTEPS / 2; kk++) {
+                    uint32_t bk[4];  // B fragments of k-steps 2kk (bk[0], bk[1]) and 2kk+1 (bk[2], bk[3])
+                    ldmatrix_x4(bk, ks + swz<D>(row0 + grp * 8 + (lane & 7), 4 * kk + (lane >> 3)));
+                    mma_16816<DT>(c0, c1, qa[2 * kk][0], qa[2 * kk][1], bk[0], bk[1]);
+                    mma_16816<DT>(c0, c1, qa[2 * kk + 1][0], qa[2 * kk + 1][1], bk[2], bk[3]);
+                }
+                const int r = row0 + grp * 8 + 2 * tq;
+                sc[2 * grp] = valid[r] ? c0 * a.scale_log2 : -INFINITY;
+                sc[2 * grp + 1] = valid[r + 1] ? c1 * a.scale_log2 : -INFINITY;
             }
-        }
-        treduce<NV, LPR>(part, lane);
-        if (writer) {
+            // ---- online softmax over the 16 rows (the 4 lanes of a head hold 4 rows each) ----
+            float mx = fmaxf(fmaxf(sc[0], sc[1]), fmaxf(sc[2], sc[3]));
+            mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 1));
+            mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 2));
+            const float m_new = fmaxf(m_run, mx);
+            const float alpha = (m_run == -INFINITY) ? 0.0f : exp2f(m_run - m_new);
+            float p[4];
 #pragma unroll
-            for (int c = 0; c < CNT; c++) {
-                const int idx = base_idx + c;       // = i * GC + g
-                const int i = idx / GC, g = idx % GC;
-                const int r = warp * WR + i * R + sub;
-                s_p[g][r] = valid[r] ? part[c] : -INFINITY;
+            for (int i = 0; i < 4; i++) p[i] = (sc[i] == -INFINITY) ? 0.0f : exp2f(sc[i] - m_new);
+            l_run = l_run * alpha + (p[0] + p[1]) + (p[2] + p[3]);
+            m_run = m_new;
+            if (__any_sync(0xFFFFFFFFu, alpha != 1.0f)) {  // the running maximum rarely moves after the first tiles
+#pragma unroll
+                for (int nt = 0; nt < NT; nt++) { o_acc[nt][0] *= alpha; o_acc[nt][1] *= alpha; }
             }
-        }
-        __syncthreads();
-
-        // ---- online softmax: warp g owns query head g ----
-        if (warp < GC) {
-            const int g = warp;
-            float mx = -INFINITY;
-            for (int r = lane; r < TILE; r += 32) mx = fmaxf(mx, s_p[g][r]);
+            // ---- O += P.V: the S fragments are the A fragments of P (k = row within the 16) ----
+            uint32_t p_hi[2], p_lo[2];
+            pack_hi_lo<DT>(p[0], p[1], p_hi[0], p_lo[0]);  // rows 2tq, 2tq+1      (k = 2tq, 2tq+1)
+            pack_hi_lo<DT>(p[2], p[3], p_hi[1], p_lo[1]);  // rows 8+2tq, 8+2tq+1  (k = 2tq+8, 2tq+9)
 #pragma unroll
-            for (int off = 16; off >= 1; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, off));
-            const float m_old = s_m[g];
-            const float m_new = fmaxf(m_old, mx);
-            float sum = 0.0f;
-            for (int r = lane; r < TILE; r += 32) {
-                float sc = s_p[g][r];
-                float p = (sc == -INFINITY) ? 0.0f : exp2f(sc - m_new);
-                s_p[g][r] = p;
-                sum += p;
-            }
-#pragma unroll
-            for (int off = 16; off >= 1; off >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, off);
-            if (lane == 0) {
-                float alpha = (m_old == -INFINITY) ? 0.0f : exp2f(m_old - m_new);
-                s_alpha[g] = alpha;
-                s_m[g] = m_new;
-                s_l[g] = s_l[g] * alpha + sum;
-            }
-        }
-        __syncthreads();
-
-        // ---- P.V ----
-#pragma unroll
-        for (int g = 0; g < GC; g++) {
-            float alpha = s_alpha[g];
-#pragma unroll
-            for (int j = 0; j < 8; j++) acc[g][j] *= alpha;
-        }
-#pragma unroll
-        for (int i = 0; i < kAttLoads; i++) {
-            const int r = warp * WR + i * R + sub;
-            const uint4 w = *reinterpret_cast<const uint4*>(vs + r * D + col * 8);
-            float f[8];
-            unpack8<DT>(w, f);
-#pragma unroll
-            for (int g = 0; g < GC; g++) {
-                float p = s_p[g][r];
-#pragma unroll
-                for (int j = 0; j < 8; j++) acc[g][j] = fmaf(p, f[j], acc[g][j]);
+            for (int n2 = 0; n2 < NT / 2; n2++) {
+                uint32_t bv[4];  // V^T fragments: (bv[0], bv[1]) for output tile 2*n2, (bv[2], bv[3]) for 2*n2+1
+                ldmatrix_x4_trans(bv, vs + swz<D>(row0 + ((lane >> 3) & 1) * 8 + (lane & 7), 2 * n2 + (lane >> 4)));
+                mma_16816<DT>(o_acc[2 * n2][0], o_acc[2 * n2][1], p_hi[0], p_hi[1], bv[0], bv[1]);
+                mma_16816<DT>(o_acc[2 * n2][0], o_acc[2 * n2][1], p_lo[0], p_lo[1], bv[0], bv[1]);
+                mma_16816<DT>(o_acc[2 * n2 + 1][0], o_acc[2 * n2 + 1][1], p_hi[0], p_hi[1], bv[2], bv[3]);
+                mma_16816<DT>(o_acc[2 * n2 + 1][0], o_acc[2 * n2 + 1][1], p_lo[0], p_lo[1], bv[2], bv[3]);
             }
         }
     }
     cp_async_wait<0>();
-    __syncthreads();  // the ring is idle: reuse it for the cross-row-group reduction
+    __syncthreads();  // the ring is idle: reuse it to merge the warps' partial results
 
-    // ---- merge the row groups' accumulators and write this split's partial ----
-    const int rg = warp * R + sub;
+    // ---- merge the kAttWarps row slices (log-sum-exp) and write this split's partial ----
+    float (*s_o)[kHeadsPerCta][D + 4] = reinterpret_cast<float (*)[kHeadsPerCta][D + 4]>(att_smem);
+    l_run += __shfl_xor_sync(0xFFFFFFFFu, l_run, 1);
+    l_run += __shfl_xor_sync(0xFFFFFFFFu, l_run, 2);
 #pragma unroll
-    for (int g = 0; g < GC; g++) {
-        *reinterpret_cast<float4*>(&s_red[rg][g][col * 8]) = make_float4(acc[g][0], acc[g][1], acc[g][2], acc[g][3]);
-        *reinterpret_cast<float4*>(&s_red[rg][g][col * 8 + 4]) = make_float4(acc[g][4], acc[g][5], acc[g][6], acc[g][7]);
-    }
+    for (int nt = 0; nt < NT; nt++)
+        *reinterpret_cast<float2*>(&s_o[warp][gq][8 * nt + 2 * tq]) = make_float2(o_acc[nt][0], o_acc[nt][1]);
+    if (tq == 0) { s_ml[warp][gq][0] = m_run; s_ml[warp][gq][1] = l_run; }
     __syncthreads();
-    for (int e = tid; e < GC * D; e += kAttThreads) {
-        int g = e / D, d = e % D;
-        if (g0 + g >= a.group) continue;
-        float s = 0.0f;
+    for (int e = tid; e < n_heads * D; e += kAttThreads) {
+        const int g = e / D, d = e % D;
+        float m = -INFINITY;
 #pragma unroll
-        for (int r = 0; r < NRG; r++) s += s_red[r][g][d];
-        a.part_acc[((prob * a.group + g0 + g) * a.n_split + split) * D + d] = s;
+        for (int w = 0; w < kAttWarps; w++) m = fmaxf(m, s_ml[w][g][0]);
+        float o = 0.0f;
+#pragma unroll
+        for (int w = 0; w < kAttWarps; w++) {
+            const float mw = s_ml[w][g][0];
+            if (mw != -INFINITY) o += s_o[w][g][d] * exp2f(mw - m);
+        }
+        a.part_acc[((prob * a.group + g0 + g) * a.n_split + split) * D + d] = o;
     }
-    if (tid < GC && g0 + tid < a.group) {
+    if (tid < n_heads) {
+        float m = -INFINITY, l = 0.0f;
+#pragma unroll
+        for (int w = 0; w < kAttWarps; w++) m = fmaxf(m, s_ml[w][tid][0]);
+#pragma unroll
+        for (int w = 0; w < kAttWarps; w++) {
+            const float mw = s_ml[w][tid][0];
+            if (mw != -INFINITY) l += s_ml[w][tid][1] * exp2f(mw - m);
+        }
         float* ml = a.part_ml + ((prob * a.group + g0 + tid) * a.n_split + split) * 2;
-        ml[0] = s_m[tid];
-        ml[1] = s_l[tid];
+        ml[0] = m;
+        ml[1] = l;
     }
 }
 
@@ -336,33 +412,22 @@ __global__ void lse_combine_kernel(const float* __restrict__ part_acc, int64_t a
     }
 }
 
-constexpr size_t kAttSmemBytes = static_cast<size_t>(kAttStages) * 2 * (kAttWarps * kAttLoads * 4) * 64 * sizeof(uint16_t);
-// = stages x (K,V) x TILE x D x 2 bytes; TILE x D = 32 lanes-rows x 8 loads x 4 warps x 8 elements for every D
-
-template <int DT, int LPR, int GC>
-int launch_attend_gc(const AttendArgs& a, dim3 grid, cudaStream_t stream) {
+template <int DT, int LPR>
+int launch_attend(const AttendArgs& a, int n_prob, cudaStream_t stream) {
     // > 48 KB of dynamic shared memory needs an opt-in per kernel and device (not a stream operation)
     static bool ready[64] = {};
     int dev = 0;
     DC_CUDA_TRY(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64 || !ready[dev]) {
-        DC_CUDA_TRY(cudaFuncSetAttribute(sparse_attend_kernel<DT, LPR, GC>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         static_cast<int>(kAttSmemBytes)));
+        DC_CUDA_TRY(cudaFuncSetAttribute(sparse_attend_kernel<DT, LPR>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(att_smem_bytes<LPR>())));
         if (dev >= 0 && dev < 64) ready[dev] = true;
     }
-    sparse_attend_kernel<DT, LPR, GC><<<grid, kAttThreads, kAttSmemBytes, stream>>>(a);
+    const int chunks = (a.group + kHeadsPerCta - 1) / kHeadsPerCta;
+    dim3 grid(static_cast<unsigned>(a.n_split), static_cast<unsigned>(n_prob), static_cast<unsigned>(chunks));
+    sparse_attend_kernel<DT, LPR><<<grid, kAttThreads, att_smem_bytes<LPR>(), stream>>>(a);
     DC_CUDA_TRY(cudaGetLastError());
     return DC_OK;
-}
-
-template <int DT, int LPR>
-int launch_attend(const AttendArgs& a, int n_prob, cudaStream_t stream) {
-    int gc = a.group >= 3 ? 4 : a.group;
-    int chunks = (a.group + gc - 1) / gc;
-    dim3 grid(static_cast<unsigned>(a.n_split), static_cast<unsigned>(n_prob), static_cast<unsigned>(chunks));
-    if (gc == 1) return launch_attend_gc<DT, LPR, 1>(a, grid, stream);
-    if (gc == 2) return launch_attend_gc<DT, LPR, 2>(a, grid, stream);
-    return launch_attend_gc<DT, LPR, 4>(a, grid, stream);
 }
 
 }  // namespace

@@ -382,33 +382,71 @@ sparse_attend_kernel(const AttendArgs a) {
 // Split-K layout (rows, n_part, D): acc_ps = D, acc_rs = n_part*D.  All-gather layout
 // (n_part, rows, D): acc_ps = part stride, acc_rs = D.  Writes either the normalised output in the
 // element type (+ optional natural-log LSE) or the merged un-normalised (acc, m, l).
+constexpr int kCombineThreads = 128;
+constexpr int kCombineMaxParts = 1024;
+
 template <int DT>
-__global__ void lse_combine_kernel(const float* __restrict__ part_acc, int64_t acc_ps, int64_t acc_rs,
-                                   const float* __restrict__ part_ml, int64_t ml_ps, int64_t ml_rs, int n_part,
-                                   int dim, uint16_t* __restrict__ out, float* __restrict__ out_lse,
-                                   float* __restrict__ out_acc, float* __restrict__ out_ml) {
+__global__ void __launch_bounds__(kCombineThreads)
+lse_combine_kernel(const float* __restrict__ part_acc, int64_t acc_ps, int64_t acc_rs,
+                   const float* __restrict__ part_ml, int64_t ml_ps, int64_t ml_rs, int n_part, int dim,
+                   uint16_t* __restrict__ out, float* __restrict__ out_lse, float* __restrict__ out_acc,
+                   float* __restrict__ out_ml) {
     const int64_t row = blockIdx.x;
-    auto ml_at = [&](int s) { return part_ml + s * ml_ps + row * ml_rs; };
-    auto acc_at = [&](int s) { return part_acc + s * acc_ps + row * acc_rs; };
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    __shared__ float s_w[kCombineMaxParts];   // weight of every part: exp2(m_s - M)
+    __shared__ float s_red[kCombineThreads / 32];
+    __shared__ float s_M, s_L;
+    const float* ml = part_ml + row * ml_rs;
+    const float* acc = part_acc + row * acc_rs;
+    // M = max_s m_s
     float m = -INFINITY;
-    for (int s = 0; s < n_part; s++) m = fmaxf(m, ml_at(s)[0]);
-    float l = 0.0f;
-    for (int s = 0; s < n_part; s++) {
-        const float* ml = ml_at(s);
-        if (ml[0] != -INFINITY) l += ml[1] * exp2f(ml[0] - m);
+    for (int s = tid; s < n_part; s += kCombineThreads) m = fmaxf(m, ml[s * ml_ps]);
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, off));
+    if (lane == 0) s_red[warp] = m;
+    __syncthreads();
+    if (tid == 0) {
+        float mm = s_red[0];
+        for (int w = 1; w < kCombineThreads / 32; w++) mm = fmaxf(mm, s_red[w]);
+        s_M = mm;
     }
-    for (int d = threadIdx.x; d < dim; d += blockDim.x) {
+    __syncthreads();
+    const float M = s_M;
+    // weights and L = sum_s w_s * l_s
+    float l = 0.0f;
+    for (int s = tid; s < n_part; s += kCombineThreads) {
+        const float ms = ml[s * ml_ps];
+        const float w = (ms == -INFINITY) ? 0.0f : exp2f(ms - M);
+        s_w[s] = w;
+        l += w * ml[s * ml_ps + 1];
+    }
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) l += __shfl_xor_sync(0xFFFFFFFFu, l, off);
+    __syncthreads();  // s_M consumed by everyone before s_red is reused; s_w complete
+    if (lane == 0) s_red[warp] = l;
+    __syncthreads();
+    if (tid == 0) {
+        float ll = 0.0f;
+        for (int w = 0; w < kCombineThreads / 32; w++) ll += s_red[w];
+        s_L = ll;
+    }
+    __syncthreads();
+    const float L = s_L;
+    for (int d = tid; d < dim; d += kCombineThreads) {
         float o = 0.0f;
-        for (int s = 0; s < n_part; s++) {
-            const float ms = ml_at(s)[0];
-            if (ms != -INFINITY) o += acc_at(s)[d] * exp2f(ms - m);
+        int s = 0;
+        for (; s + 4 <= n_part; s += 4) {  // four independent loads in flight
+            const float a0 = acc[(s + 0) * acc_ps + d], a1 = acc[(s + 1) * acc_ps + d];
+            const float a2 = acc[(s + 2) * acc_ps + d], a3 = acc[(s + 3) * acc_ps + d];
+            o += a0 * s_w[s] + a1 * s_w[s + 1] + a2 * s_w[s + 2] + a3 * s_w[s + 3];
         }
-        if (out) out[row * dim + d] = float_to_elem<DT>(l > 0.0f ? o / l : 0.0f);
+        for (; s < n_part; s++) o += acc[s * acc_ps + d] * s_w[s];
+        if (out) out[row * dim + d] = float_to_elem<DT>(L > 0.0f ? o / L : 0.0f);
         if (out_acc) out_acc[row * dim + d] = o;
     }
-    if (threadIdx.x == 0) {
-        if (out_lse) out_lse[row] = l > 0.0f ? (m + log2f(l)) * 0.6931471805599453f : -INFINITY;
-        if (out_ml) { out_ml[row * 2] = m; out_ml[row * 2 + 1] = l; }
+    if (tid == 0) {
+        if (out_lse) out_lse[row] = L > 0.0f ? (M + log2f(L)) * 0.6931471805599453f : -INFINITY;
+        if (out_ml) { out_ml[row * 2] = M; out_ml[row * 2 + 1] = L; }
     }
 }
 
@@ -456,8 +494,9 @@ int lse_combine(const float* acc, int64_t acc_ps, int64_t acc_rs, const float* m
                 float* out_ml, cudaStream_t stream) {
     DC_REQUIRE(acc && ml && n_part >= 1 && rows >= 0, "lse_combine: bad arguments");
     DC_REQUIRE(dtype == DC_BF16 || dtype == DC_FP16, "lse_combine: dtype %d not supported", dtype);
+    DC_REQUIRE(n_part <= kCombineMaxParts, "lse_combine: n_part=%d exceeds %d", n_part, kCombineMaxParts);
     if (rows == 0) return DC_OK;
-    int threads = std::min(256, ((head_dim + 31) / 32) * 32);
+    const int threads = kCombineThreads;
     if (dtype == DC_BF16)
         lse_combine_kernel<DC_BF16><<<static_cast<unsigned>(rows), threads, 0, stream>>>(
             acc, acc_ps, acc_rs, ml, ml_ps, ml_rs, n_part, head_dim, static_cast<uint16_t*>(out), out_lse, out_acc,

@@ -162,6 +162,40 @@ __device__ __forceinline__ int treduce_base(int lane) {
     return base;
 }
 
+
+// ---- asynchronous bulk copies (TMA engine, untiled form) completing on a shared-memory mbarrier ----
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return static_cast<unsigned>(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ void mbar_init(unsigned long long* bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_init_fence() { asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory"); }
+__device__ __forceinline__ void mbar_arrive_expect_tx(unsigned long long* bar, unsigned bytes) {
+    asm volatile("{\n .reg .b64 st;\n mbarrier.arrive.expect_tx.shared::cta.b64 st, [%0], %1;\n}\n"
+                 ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(unsigned long long* bar, unsigned parity) {
+    unsigned ok;
+    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+                 : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait: gives up after kMbarSpinLimit polls (each poll itself blocks for a hardware-defined
+// time slice), so a copy that never completes cannot hang the GPU; the caller reports the failure.
+constexpr int kMbarSpinLimit = 1 << 20;
+__device__ __forceinline__ bool mbar_wait_bounded(unsigned long long* bar, unsigned parity) {
+    for (int i = 0; i < kMbarSpinLimit; i++)
+        if (mbar_try_wait(bar, parity)) return true;
+    return false;
+}
+// One thread copies `bytes` (a multiple of 16; both addresses 16-byte aligned) global -> shared;
+// completion is signalled on `bar` as `bytes` transaction bytes.
+__device__ __forceinline__ void bulk_copy_g2s(void* smem_dst, const void* gmem_src, unsigned bytes, unsigned long long* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n"
+                 ::"r"(smem_u32(smem_dst)), "l"(gmem_src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+// Orders this thread's earlier generic-proxy shared-memory accesses before later async-proxy ones.
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
+
 // Ranking key of the reference: raw bits of fp32 (65536 - dot).
 __device__ __forceinline__ uint32_t dist_bits(float dot) { return __float_as_uint(65536.0f - dot); }
 

@@ -52,13 +52,32 @@ def shard_heads(kv_heads: int, world: int) -> List[Tuple[int, int]]:
     return [(r * per, per) for r in range(world)]
 
 
+def _adjacent(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """``stack([a, b])``; free when ``b`` already sits right behind ``a`` in one allocation."""
+    if (a.is_contiguous() and b.is_contiguous() and a.dtype == b.dtype and a.shape == b.shape
+            and a.untyped_storage().data_ptr() == b.untyped_storage().data_ptr()
+            and b.storage_offset() == a.storage_offset() + a.numel()):
+        return torch.as_strided(a, (2,) + tuple(a.shape), (a.numel(),) + tuple(a.stride()))
+    return torch.stack([a, b])
+
+
+def _adjacent_flat(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """``cat([a.flatten(), b.flatten()])``; free when ``b`` sits right behind ``a`` in one allocation."""
+    if (a.is_contiguous() and b.is_contiguous() and a.dtype == b.dtype
+            and a.untyped_storage().data_ptr() == b.untyped_storage().data_ptr()
+            and b.storage_offset() == a.storage_offset() + a.numel()):
+        return torch.as_strided(a, (a.numel() + b.numel(),), (1,))
+    return torch.cat([a.reshape(-1), b.reshape(-1)])
+
+
 class SequenceShardedStep:
     """Sequence-sharded fused decode step.  ``backend`` provides
 
     ``local_topk(q, k) -> (bits, gidx)``  int32/uint32-pattern tensors ``(P, k)``, padded with 0xFFFFFFFF
     ``merge(bits_all, gidx_all, k) -> sel``  ``(P, k)`` global row ids from ``(P, world*k)`` candidates
     ``attend_owned(q, sel) -> (acc, ml)``  fp32 ``(P*G, D)`` and ``(P*G, 2)``
-    ``combine(acc_all, ml_all) -> out``  from ``(world, P*G, D)`` / ``(world, P*G, 2)``
+    ``combine_packed(parts, rows, D) -> out``  from ``(world, rows*D + rows*2)``: per rank the accumulators
+    followed by the (max, sum) pairs
     """
 
     def __init__(self, backend, topk: int, group: Optional["dist.ProcessGroup"] = None):
@@ -77,17 +96,21 @@ class SequenceShardedStep:
         return out.view((self.world,) + tuple(t.shape))
 
     def step(self, q: torch.Tensor) -> torch.Tensor:
+        """Two exchanges per step: the candidates (one buffer holding bits and ids) and the partial
+        attention results (one buffer holding accumulators and (max, sum) pairs)."""
         k = self.topk
         bits, gidx = self.backend.local_topk(q, k)                       # (P, k) each
-        cand = self._all_gather(torch.stack([bits, gidx]))               # (world, 2, P, k)
+        packed = _adjacent(bits, gidx)                                   # (2, P, k) without a copy when possible
+        cand = self._all_gather(packed)                                  # (world, 2, P, k)
         P = bits.shape[0]
         cand = cand.permute(1, 2, 0, 3).reshape(2, P, self.world * k).contiguous()
         sel = self.backend.merge(cand[0], cand[1], k)                    # (P, k) global ids, identical on all ranks
         acc, ml = self.backend.attend_owned(q, sel)
-        acc_all = self._all_gather(acc)                                  # (world, P*G, D)
-        ml_all = self._all_gather(ml)                                    # (world, P*G, 2)
+        rows, D = acc.shape
+        flat = _adjacent_flat(acc, ml)                                   # [acc | ml] as one flat buffer
+        parts = self._all_gather(flat)                                   # (world, rows*D + rows*2)
         self.last_selection = sel
-        return self.backend.combine(acc_all, ml_all)
+        return self.backend.combine_packed(parts, rows, D)
 
 
 class GpuShardBackend:
@@ -120,8 +143,8 @@ class GpuShardBackend:
         return int(torch.cuda.current_stream().cuda_stream)
 
     def local_topk(self, q, k):
-        bits = self._buf("bits", (self.P, k), torch.int32)
-        gidx = self._buf("gidx", (self.P, k), torch.int32)
+        both = self._buf("cand", (2, self.P, k), torch.int32)
+        bits, gidx = both[0], both[1]
         self.e.local_topk(q, k, bits, gidx)
         return bits, gidx
 
@@ -133,15 +156,18 @@ class GpuShardBackend:
         return sel
 
     def attend_owned(self, q, sel):
-        acc = self._buf("acc", (self.P * self.G, self.D), torch.float32)
-        ml = self._buf("ml", (self.P * self.G, 2), torch.float32)
+        rows = self.P * self.G
+        flat = self._buf("partial", (rows * (self.D + 2),), torch.float32)
+        acc = flat[:rows * self.D].view(rows, self.D)
+        ml = flat[rows * self.D:].view(rows, 2)
         self.e.attend_owned(q, sel, sel.shape[1], acc, ml, res_k=self.res_k, res_v=self.res_v, res_len=self.res_len,
                             k_new=self.k_new, v_new=self.v_new, scale=self.scale)
         return acc, ml
 
-    def combine(self, acc_all, ml_all):
-        world, rows, D = acc_all.shape
+    def combine_packed(self, parts, rows, D):
+        world = parts.shape[0]
+        stride = rows * (D + 2)
         out = self._buf("out", (self.e.bsz, self.e.q_head_num, D), torch.bfloat16 if self.e.dtype == 0 else torch.float16)
-        _lib.check(self.lib.dc_lse_combine(acc_all.data_ptr(), rows * D, ml_all.data_ptr(), rows * 2, world, rows, D,
-                                           self.e.dtype, out.data_ptr(), None, self._stream()))
+        _lib.check(self.lib.dc_lse_combine(parts.data_ptr(), stride, parts.data_ptr() + rows * D * 4, stride, world, rows,
+                                           D, self.e.dtype, out.data_ptr(), None, self._stream()))
         return out

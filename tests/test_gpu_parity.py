@@ -446,9 +446,8 @@ def test_sequence_sharded_step_emulated_on_one_gpu(oracle_lib):
     cand = torch.stack(cands).permute(1, 2, 0, 3).reshape(2, P, world * topk).contiguous()
     sels = [b.merge(cand[0], cand[1], topk).clone() for b in backends]
     assert all(torch.equal(sels[0], s) for s in sels)
-    parts_out = [tuple(t.clone() for t in b.attend_owned(qd, sels[0])) for b in backends]
-    out = backends[0].combine(torch.stack([a for a, _ in parts_out]).contiguous(),
-                              torch.stack([m for _, m in parts_out]).contiguous())
+    parts_out = [torch.cat([t.reshape(-1) for t in b.attend_owned(qd, sels[0])]) for b in backends]
+    out = backends[0].combine_packed(torch.stack(parts_out).contiguous(), P * G, D)
     for e in engines:
         e.check_status()
     torch.cuda.synchronize()
@@ -521,3 +520,69 @@ def test_pq_adc_rerank_path(lib, oracle_lib):
         wb, wi = oracle_lib.topk(rb, topk, ids=ci, method="sort")
         all_bits = oracle_lib.score_rows(ku[p], qm[p], 0)
         util.check_selection_parity(sel_idx[p].cpu().numpy(), wi, all_bits)
+
+
+def test_full_size_configuration_1_properties(oracle_lib):
+    """Configuration 1 at its full size (batch 16, 128K context, top-k 2048 + 64 sink + 512 window):
+    the fused step is checked through properties that do not need the oracle to scan 16.7 M rows —
+    (a) for every problem the selected rows are exactly the k best of the GPU's own ranking keys
+    (selection is bit-exact integer work), (b) the ranking keys of sampled rows equal the oracle's
+    within one ulp of dist, and (c) for a few whole problems selection and attention output match
+    the oracle end to end."""
+    from diffcache_b200 import DiffCacheGPU, _lib, synth
+
+    free, _ = torch.cuda.mem_get_info()
+    if free < 40 * 2 ** 30:
+        pytest.skip("needs 40 GB of free device memory")
+    lib = _lib.load()
+    cfg = synth.CONFIGS["cfg1"]
+    B, Hkv, G, D, n_r, topk = cfg.batch, cfg.kv_heads, cfg.group, cfg.head_dim, cfg.n_retrieval, cfg.topk
+    P = B * Hkv
+    dev = torch.device("cuda", torch.cuda.current_device())
+    k, v = synth.make_kv(B, Hkv, cfg.context, D, 1000, cfg.dtype, device=dev)
+    q = synth.make_query(k[:, :, cfg.sink:cfg.sink + n_r], G, 1000).contiguous()
+    eng = DiffCacheGPU(B, cfg.q_heads, Hkv, D, max_ctx_len=n_r)
+    eng.prefill(k[:, :, cfg.sink:cfg.sink + n_r], v[:, :, cfg.sink:cfg.sink + n_r])
+    res_rows = cfg.sink + cfg.window - 1
+    rk = torch.zeros((B, Hkv, cfg.sink + cfg.window + 8, D), dtype=torch.bfloat16, device=dev)
+    rv = torch.zeros_like(rk)
+    for dst, src in ((rk, k), (rv, v)):
+        dst[:, :, :cfg.sink] = src[:, :, :cfg.sink]
+        dst[:, :, cfg.sink:res_rows] = src[:, :, cfg.sink + n_r:cfg.context - 1]
+    kn, vn = k[:, :, -1].contiguous(), v[:, :, -1].contiguous()
+    out, idx, _ = _run_decode(eng, q, rk, rv, res_rows, kn, vn, topk)
+    gi = idx.cpu().numpy().reshape(P, topk).astype(np.int64)
+
+    # (a) the GPU's own keys, all problems: top-k of (bits, id) by a host sort
+    ks = k[:, :, cfg.sink:cfg.sink + n_r].reshape(P, n_r, D)  # view of the generated keys (same bytes as the store)
+    scores = torch.zeros((P, n_r), dtype=torch.int32, device=dev)
+    rc = lib.dc_score_scan(ks.contiguous().data_ptr(), n_r * D, P, n_r, D, 0, q.data_ptr(), 1, G, scores.data_ptr(), n_r,
+                           None, _stream())
+    assert rc == 0, lib.dc_last_error()
+    torch.cuda.synchronize()
+    sc = scores.cpu().numpy().view(np.uint32)
+    for p in range(P):
+        keys = (sc[p].astype(np.uint64) << np.uint64(32)) | np.arange(n_r, dtype=np.uint64)
+        want = np.sort(np.partition(keys, topk - 1)[:topk])
+        got = (sc[p][gi[p]].astype(np.uint64) << np.uint64(32)) | gi[p].astype(np.uint64)
+        assert np.array_equal(got, want), f"problem {p}: selection is not the top-k of the GPU keys"
+
+    # (b) + (c) three whole problems against the oracle
+    qh = util.u16(q).reshape(P * G, D)
+    qm = oracle_lib.group_mean(qh, G, 0)
+    for p in (0, 57, P - 1):
+        b, h = divmod(p, Hkv)
+        kp = util.u16(ks[p])
+        vp = util.u16(v[b, h, cfg.sink:cfg.sink + n_r])
+        all_bits = oracle_lib.score_rows(kp, qm[p], 0)
+        ulp = util.ulp_of_dist(all_bits)
+        diff = np.abs(sc[p].view(np.float32).astype(np.float64) - all_bits.view(np.float32).astype(np.float64))
+        assert np.all(diff <= ulp) and np.mean(sc[p] == all_bits) > 0.9
+        ref = oracle_lib.query(kp[None], vp[None], qm[p:p + 1], topk, 0)
+        subs = util.check_selection_parity(gi[p], ref["idx"][0], all_bits)
+        if subs == 0:
+            rows_k = np.concatenate([ref["keys"][0], util.u16(rk[b, h, :res_rows]), util.u16(kn[b, h])[None]])
+            rows_v = np.concatenate([ref["vals"][0], util.u16(rv[b, h, :res_rows]), util.u16(vn[b, h])[None]])
+            of, _, _ = oracle_lib.attend(rows_k[None], rows_v[None], qh[p * G:(p + 1) * G], G, D ** -0.5, 0)
+            util.assert_attention_close(util.u16(out[b, h * G:(h + 1) * G]), of, 0, oracle_lib, ATOL, RTOL)
+    eng.close()

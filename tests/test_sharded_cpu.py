@@ -80,8 +80,11 @@ class OracleShardBackend:
                 ml[r] = (m, w.sum())
         return torch.from_numpy(acc), torch.from_numpy(ml)
 
-    def combine(self, acc_all, ml_all):
-        a, m = acc_all.numpy().astype(np.float64), ml_all.numpy().astype(np.float64)
+    def combine_packed(self, parts, rows, D):
+        parts = parts.numpy()
+        acc_all = parts[:, :rows * D].reshape(-1, rows, D)
+        ml_all = parts[:, rows * D:].reshape(-1, rows, 2)
+        a, m = acc_all.astype(np.float64), ml_all.astype(np.float64)
         mx = m[..., 0].max(axis=0)
         with np.errstate(invalid="ignore"):
             w = np.where(np.isinf(m[..., 0]), 0.0, np.exp2(m[..., 0] - mx))

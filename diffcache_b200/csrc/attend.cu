@@ -34,6 +34,7 @@ struct AttendArgs {
     int64_t sel_stride;
     int n_sel;
     int64_t sel_base;      // id - sel_base = local row; ids outside [0, n_rows) are skipped
+    const int32_t* sel_count;  // optional per-problem budget: only the first sel_count[p] ids are attended
     const uint16_t* k_new; // (n_prob, D) or nullptr
     const uint16_t* v_new;
     uint16_t* res_k;       // resident rows
@@ -183,6 +184,7 @@ sparse_attend_kernel(const AttendArgs a) {
     uint16_t* rk = a.res_k ? a.res_k + b * a.res_stride_b + h * a.res_stride_h : nullptr;
     uint16_t* rv = a.res_v ? a.res_v + b * a.res_stride_b + h * a.res_stride_h : nullptr;
     const uint32_t* selp = a.sel ? a.sel + prob * a.sel_stride : nullptr;
+    const int n_sel_eff = a.sel_count ? min(a.n_sel, a.sel_count[prob]) : a.n_sel;  // rows beyond it are skipped
 
     // flash-attn's in-place append of the new token (base.py:134-142): one CTA per problem
     if (has_new && split == 0 && blockIdx.z == 0 && rk != nullptr && tid < LPR) {
@@ -197,7 +199,7 @@ sparse_attend_kernel(const AttendArgs a) {
 #pragma unroll
         for (int i = 0; i < NCOPY; i++) {
             const int j = j0 + t * TILE + warp * RW + i * R + sub;
-            ids[i] = (t < n_tiles && j < j1 && j < a.n_sel) ? selp[j] : 0xFFFFFFFFu;
+            ids[i] = (t < n_tiles && j < j1 && j < n_sel_eff) ? selp[j] : 0xFFFFFFFFu;
         }
     };
     // Issue the copies of tile `t` into its ring slot (one commit group per call, possibly empty).
@@ -513,7 +515,8 @@ int sparse_attend(const void* k_store, const void* v_store, int64_t prob_stride,
                   int kv_heads, int group, int head_dim, int dtype, const void* q, const uint32_t* sel,
                   int64_t sel_stride, int n_sel, int64_t sel_base, const void* k_new, const void* v_new, void* res_k,
                   void* res_v, int64_t res_stride_b, int64_t res_stride_h, int res_len, float scale, void* out,
-                  float* out_lse, float* out_acc, float* out_ml, void* scratch, cudaStream_t stream) {
+                  float* out_lse, float* out_acc, float* out_ml, void* scratch, cudaStream_t stream,
+                  const int32_t* sel_count) {
     DC_REQUIRE(q != nullptr && scratch != nullptr, "sparse_attend: null q/scratch");
     DC_REQUIRE(dtype == DC_BF16 || dtype == DC_FP16, "sparse_attend: dtype %d not supported", dtype);
     DC_REQUIRE(head_dim == 64 || head_dim == 128 || head_dim == 256, "sparse_attend: head_dim %d not in {64,128,256}",
@@ -549,6 +552,7 @@ int sparse_attend(const void* k_store, const void* v_store, int64_t prob_stride,
     a.sel_stride = sel_stride;
     a.n_sel = n_sel;
     a.sel_base = sel_base;
+    a.sel_count = sel_count;
     a.k_new = static_cast<const uint16_t*>(k_new);
     a.v_new = static_cast<const uint16_t*>(v_new);
     a.res_k = static_cast<uint16_t*>(res_k);
@@ -653,5 +657,5 @@ extern "C" int dc_sparse_attend_noalloc(const void* k_store, const void* v_store
     if (rc != DC_OK) return rc;
     return sparse_attend(k_store, v_store, prob_stride, n_rows, n_prob, kv_heads, group, head_dim, dtype, q, sel,
                          sel_stride, n_sel, sel_base, k_new, v_new, res_k, res_v, res_stride_b, res_stride_h, res_len,
-                         scale, out, out_lse, out_acc, out_ml, scratch, as_stream(stream));
+                         scale, out, out_lse, out_acc, out_ml, scratch, as_stream(stream), nullptr);
 }

@@ -27,7 +27,10 @@ int sparse_attend(const void* k_store, const void* v_store, int64_t prob_stride,
                   int kv_heads, int group, int head_dim, int dtype, const void* q, const uint32_t* sel,
                   int64_t sel_stride, int n_sel, int64_t sel_base, const void* k_new, const void* v_new, void* res_k,
                   void* res_v, int64_t res_stride_b, int64_t res_stride_h, int res_len, float scale, void* out,
-                  float* out_lse, float* out_acc, float* out_ml, void* scratch, cudaStream_t stream);
+                  float* out_lse, float* out_acc, float* out_ml, void* scratch, cudaStream_t stream,
+                  const int32_t* sel_count = nullptr);
+int adaptive_budget(const uint32_t* bits, int64_t stride, int n_prob, int k, int head_dim, const int* seq, int n_seq,
+                    float threshold, int32_t* budget, cudaStream_t stream);
 int64_t attend_scratch_bytes(int n_prob, int group, int head_dim);
 int lse_combine(const float* acc, int64_t acc_ps, int64_t acc_rs, const float* ml, int64_t ml_ps, int64_t ml_rs,
                 int n_part, int64_t rows, int head_dim, int dtype, void* out, float* out_lse, float* out_acc,
@@ -147,6 +150,10 @@ struct dc_engine {
     int64_t stage_rows = 0;
     std::vector<cudaEvent_t> phase_events;  // 4 per timed step: before scan, after scan, after select, after attend
     int phase_cap = 0, phase_count = 0;
+    int32_t* budget = nullptr;     // per-problem adaptive budget (k-check), n_prob entries
+    int budget_seq[16] = {};
+    int budget_n = 0;              // 0 = adaptive budget off
+    float budget_threshold = 0.9f;
 };
 
 namespace {
@@ -285,6 +292,7 @@ int dc_create(int bsz, int q_heads, int kv_heads, int head_dim, int64_t max_ctx_
     alloc(reinterpret_cast<void**>(&e->sel_idx), static_cast<size_t>(e->n_prob) * sel_cap * sizeof(uint32_t));
     alloc(reinterpret_cast<void**>(&e->sel_bits), static_cast<size_t>(e->n_prob) * sel_cap * sizeof(uint32_t));
     alloc(reinterpret_cast<void**>(&e->status), 256);
+    alloc(reinterpret_cast<void**>(&e->budget), static_cast<size_t>(e->n_prob) * sizeof(int32_t));
     alloc(&e->att_scratch, static_cast<size_t>(attend_scratch_bytes(e->n_prob, e->group, head_dim)));
     alloc(reinterpret_cast<void**>(&e->q_dev), static_cast<size_t>(bsz) * q_heads * head_dim * sizeof(uint16_t));
     if (err == cudaSuccess) err = cudaMemset(e->status, 0, 256);
@@ -306,7 +314,7 @@ int dc_destroy(dc_engine* e) {
     DeviceGuard guard(e->device);
     cudaDeviceSynchronize();
     cudaFree(e->k); cudaFree(e->v); cudaFree(e->scores); cudaFree(e->minmax); cudaFree(e->sel_idx);
-    cudaFree(e->sel_bits); cudaFree(e->status); cudaFree(e->att_scratch); cudaFree(e->q_dev);
+    cudaFree(e->sel_bits); cudaFree(e->status); cudaFree(e->budget); cudaFree(e->att_scratch); cudaFree(e->q_dev);
     cudaFree(e->stage_k); cudaFree(e->stage_v);
     for (cudaEvent_t ev : e->phase_events) cudaEventDestroy(ev);
     cudaGetLastError();
@@ -482,9 +490,16 @@ int dc_decode_attend(dc_engine* e, const void* q, const void* k_new, const void*
         rc = scan_and_select(e, q, 1, k, 0u, e->sel_bits, e->sel_idx, s, ev);
         if (rc) return rc;
     }
+    const int32_t* sel_count = nullptr;
+    if (k > 0 && e->budget_n > 0) {  // k-check epilogue of the select: rows beyond the budget are not attended
+        rc = adaptive_budget(e->sel_bits, k, e->n_prob, k, e->head_dim, e->budget_seq, e->budget_n, e->budget_threshold,
+                             e->budget, s);
+        if (rc) return rc;
+        sel_count = e->budget;
+    }
     rc = sparse_attend(e->k, e->v, e->prob_stride, e->ctx_len, e->n_prob, e->kv_heads, e->group, e->head_dim, e->dtype,
                        q, e->sel_idx, k, k, 0, k_new, v_new, res_k, res_v, res_stride_b, res_stride_h, res_len, scale,
-                       out, out_lse, nullptr, nullptr, e->att_scratch, s);
+                       out, out_lse, nullptr, nullptr, e->att_scratch, s, sel_count);
     if (rc) return rc;
     if (ev) {
         DC_CUDA_TRY(cudaEventRecord(ev[3], s));
@@ -494,6 +509,36 @@ int dc_decode_attend(dc_engine* e, const void* q, const void* k_new, const void*
         DC_CUDA_TRY(cudaMemcpyAsync(out_idx, e->sel_idx, static_cast<size_t>(e->n_prob) * k * sizeof(uint32_t),
                                     cudaMemcpyDeviceToDevice, s));
     return DC_OK;
+}
+
+int dc_set_adaptive_budget(dc_engine* e, const int32_t* k_check_seq, int n_seq, float attn_mass_threshold) {
+    DC_ENGINE_ENTER(e);
+    DC_REQUIRE(n_seq >= 0 && n_seq <= 16, "dc_set_adaptive_budget: at most 16 checkpoints (got %d)", n_seq);
+    DC_REQUIRE(n_seq == 0 || k_check_seq != nullptr, "dc_set_adaptive_budget: null k_check_seq");
+    for (int i = 0; i < n_seq; i++) {
+        DC_REQUIRE(k_check_seq[i] >= 1 && (i == 0 || k_check_seq[i] > k_check_seq[i - 1]),
+                   "dc_set_adaptive_budget: k_check_seq must be positive and increasing");
+        e->budget_seq[i] = k_check_seq[i];
+    }
+    e->budget_n = n_seq;
+    e->budget_threshold = attn_mass_threshold;
+    return DC_OK;
+}
+
+int dc_get_budget(dc_engine* e, int32_t* out, uint64_t stream) {
+    DC_ENGINE_ENTER(e);
+    DC_REQUIRE(out != nullptr, "dc_get_budget: null out");
+    DC_CUDA_TRY(cudaMemcpyAsync(out, e->budget, static_cast<size_t>(e->n_prob) * sizeof(int32_t), cudaMemcpyDefault,
+                                as_stream(stream)));
+    if (!is_device_ptr(out)) DC_CUDA_TRY(cudaStreamSynchronize(as_stream(stream)));
+    return DC_OK;
+}
+
+int dc_adaptive_budget(const uint32_t* sel_bits, int64_t stride, int n_prob, int k, int head_dim,
+                       const int32_t* k_check_seq, int n_seq, float attn_mass_threshold, int32_t* out_budget,
+                       uint64_t stream) {
+    return adaptive_budget(sel_bits, stride, n_prob, k, head_dim, k_check_seq, n_seq, attn_mass_threshold, out_budget,
+                           as_stream(stream));
 }
 
 int dc_set_phase_timing(dc_engine* e, int max_steps) {

@@ -91,11 +91,13 @@ class DiffCacheGPU:
     The graph parameters are accepted and ignored: this engine always runs the exact
     scan, i.e. the reference's ``use_bruteforce=True`` semantics.  Two keyword-only
     additions select the element type and device: ``dtype`` ("bf16" | "fp16") and
-    ``device`` (CUDA ordinal)."""
+    ``device`` (CUDA ordinal); ``adaptive_budget=True`` applies the reference's k-check
+    (``k_check_seq``, ``attn_mass_threshold``) to the fused step."""
 
     def __init__(self, bsz: int, q_head_num: int, kv_head_num: int, head_dim: int, **kwargs):
         dtype = kwargs.pop("dtype", "bf16")
         device = kwargs.pop("device", None)
+        adaptive = bool(kwargs.pop("adaptive_budget", False))
         opts = dict(_OPTION_DEFAULTS)
         for key, value in kwargs.items():
             if key not in opts:
@@ -118,6 +120,8 @@ class DiffCacheGPU:
         _lib.check(self._lib.dc_create(bsz, q_head_num, kv_head_num, head_dim, int(opts["max_ctx_len"]), self.dtype,
                                        self.device, ctypes.byref(handle)))
         self._h = handle
+        if adaptive:
+            self.set_adaptive_budget(opts["k_check_seq"], opts["attn_mass_threshold"])
 
     # -- lifetime ------------------------------------------------------------------------
     def close(self) -> None:
@@ -261,6 +265,20 @@ class DiffCacheGPU:
         _lib.check(self._lib.dc_decode_attend(self._h, _ptr(q), _ptr(k_new), _ptr(v_new), _ptr(res_k), _ptr(res_v), sb,
                                               sh, int(res_len), int(topk), float(scale), _ptr(out), _ptr(out_idx),
                                               _ptr(out_lse), _current_stream(stream)))
+
+    def set_adaptive_budget(self, k_check_seq, attn_mass_threshold: float) -> None:
+        """Switch the k-check on for ``decode_attend`` (``k_check_seq`` empty switches it off): per
+        (batch, kv-head) the first checkpoint whose top-h keys already hold ``attn_mass_threshold`` of
+        the estimated attention mass becomes the number of retrieved rows attended (nsw.rs:198-300)."""
+        seq = np.asarray(sorted(int(x) for x in k_check_seq)[:16], np.int32)
+        _lib.check(self._lib.dc_set_adaptive_budget(self._h, seq.ctypes.data if seq.size else None, int(seq.size),
+                                                    float(attn_mass_threshold)))
+
+    def last_budget(self) -> np.ndarray:
+        """Budgets chosen by the last ``decode_attend`` step, ``(bsz, kv_head_num)`` int32."""
+        out = np.zeros((self.bsz, self.kv_head_num), np.int32)
+        _lib.check(self._lib.dc_get_budget(self._h, out.ctypes.data, _current_stream(None)))
+        return out
 
     def set_phase_timing(self, max_steps: int) -> None:
         """Record CUDA events around the scan / select / attend phases of the next ``max_steps``

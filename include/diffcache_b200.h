@@ -175,6 +175,21 @@ int dc_decode_attend(dc_engine* e, const void* q, const void* k_new, const void*
                      float* out_lse, uint64_t stream);
 
 /*
+ * Adaptive retrieval budget.  Replaces the k-check early stop of the reference's
+ * search (fit_alpha_from_logits / estimate_top_h_mass / k_check_early_stoppable,
+ * diffcache_cpu/src/nsw.rs:198-300, applied at the checkpoints of `k_check_seq`,
+ * nsw.rs:339-376; options `k_check_seq`, `attn_mass_threshold`, lib.rs:565-566):
+ * after the exact top-k, per problem the first checkpoint h < topk whose top-h
+ * logits (65536 - dist) / sqrt(head_dim) pass the power-law mass test becomes the
+ * budget, and dc_decode_attend attends only over the h best rows (plus resident
+ * rows and the new token).  n_seq = 0 switches it off (default).  The test runs
+ * on the device; dc_get_budget copies the (bsz*kv_heads) int32 budgets of the
+ * last step (host or device destination).
+ */
+int dc_set_adaptive_budget(dc_engine* e, const int32_t* k_check_seq, int n_seq, float attn_mass_threshold);
+int dc_get_budget(dc_engine* e, int32_t* out, uint64_t stream);
+
+/*
  * Per-phase device timing of dc_decode_attend, the counterpart of the reference's
  * `{name}_search_latency` / `{name}_collect_latency` / `{name}_total_query_latency`
  * counters (diffcache_cpu/src/nsw.rs:618,660, diffcache_cpu/src/lib.rs:403).
@@ -306,6 +321,15 @@ int dc_sparse_attend_noalloc(const void* k_store, const void* v_store, int64_t p
 int dc_lse_combine(const float* acc, int64_t acc_part_stride, const float* ml, int64_t ml_part_stride,
                    int n_part, int64_t rows, int head_dim, int dtype, void* out, float* out_lse,
                    uint64_t stream);
+
+/*
+ * The k-check on its own: sel_bits (n_prob, stride) best-first ranking keys as
+ * written by dc_topk_select, k of them valid per problem; out_budget (n_prob)
+ * int32 on the device; k_check_seq is a host array (nsw.rs:198-300,339-376).
+ */
+int dc_adaptive_budget(const uint32_t* sel_bits, int64_t stride, int n_prob, int k, int head_dim,
+                       const int32_t* k_check_seq, int n_seq, float attn_mass_threshold, int32_t* out_budget,
+                       uint64_t stream);
 
 /* Gather rows: out[p][i][:] = store[p][ids[p][i]][:]  (nsw.rs:623-629). */
 int dc_gather_rows(const void* store, int64_t prob_stride, int n_prob, int head_dim,

@@ -59,6 +59,10 @@ def lib() -> ctypes.CDLL:
         _lib.dco_pq_build_lut.argtypes = [vp, i32, vp, i32, i32, i32, vp]
         _lib.dco_pq_adc_scores.argtypes = [vp, i64, i32, vp, vp]
         _lib.dco_rerank_scores.argtypes = [vp, i32, i32, vp, vp, i64, i32, vp]
+        _lib.dco_k_check.argtypes = [vp, i32, i32, f32, vp, vp]
+        _lib.dco_k_check.restype = i32
+        _lib.dco_adaptive_budget.argtypes = [vp, i32, i32, vp, i32, f32]
+        _lib.dco_adaptive_budget.restype = i32
         _lib.dco_max_threads.restype = i32
     return _lib
 
@@ -185,3 +189,19 @@ def rerank_scores(keys_u16, q_u16, ids_u32, dtype: int, exact: bool = True) -> n
     out = np.empty(ids.shape[0], np.uint32)
     lib().dco_rerank_scores(_p(k), k.shape[1], dtype, _p(q), _p(ids), ids.shape[0], int(exact), _p(out))
     return out
+
+
+def k_check(dist_bits_sorted: np.ndarray, dim: int, threshold: float):
+    """nsw.rs:285-300 on the best-first ranking keys; returns (stoppable, alpha, mass)."""
+    b = _c(dist_bits_sorted, np.uint32)
+    alpha = np.zeros(1, np.float32)
+    mass = np.zeros(1, np.float32)
+    ok = lib().dco_k_check(_p(b), b.shape[0], dim, threshold, _p(alpha), _p(mass))
+    return bool(ok), float(alpha[0]), float(mass[0])
+
+
+def adaptive_budget(dist_bits_sorted: np.ndarray, dim: int, seq, threshold: float) -> int:
+    """First checkpoint of k_check_seq whose top-h keys pass the k-check, else k (nsw.rs:339-376)."""
+    b = _c(dist_bits_sorted, np.uint32)
+    sq = np.asarray(list(seq), np.int32)
+    return int(lib().dco_adaptive_budget(_p(b), b.shape[0], dim, _p(sq), sq.shape[0], threshold))

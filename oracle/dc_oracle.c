@@ -380,3 +380,77 @@ int dco_max_threads(void) {
     return 1;
 #endif
 }
+
+/* ---- adaptive budget ("k-check"): power-law estimate of the attention mass of the top-h keys ---- */
+
+/*
+ * fit_alpha_from_logits (diffcache_cpu/src/nsw.rs:198-246): least-squares fit of
+ * logit = a + b*ln(rank) over ranks min_rank..h (1-based), alpha = -b.  Sums in
+ * double, alpha returned as float.  Returns 0 where the reference returns None.
+ */
+int dco_fit_alpha(const float* logits_sorted, int h, int min_rank, float* alpha_out) {
+    if (h == 0 || min_rank == 0 || min_rank >= h) return 0;
+    double n = (double)(h - min_rank + 1);
+    if (n < 2.0) return 0;
+    double sx = 0, sy = 0, sxx = 0, sxy = 0;
+    for (int idx = min_rank - 1; idx < h; idx++) {
+        double x = log((double)(idx + 1));
+        double y = (double)logits_sorted[idx];
+        sx += x; sy += y; sxx += x * x; sxy += x * y;
+    }
+    double denom = n * sxx - sx * sx;
+    if (fabs(denom) < 1e-12) return 0;
+    double b = (n * sxy - sx * sy) / denom;
+    *alpha_out = (float)(-b);
+    return 1;
+}
+
+/*
+ * estimate_top_h_mass (nsw.rs:248-283): head = sum_{i<h} exp(z_i - max), tail =
+ * exp(z_h - max) * h / (alpha - 1), mass = head / (head + tail); fp32 arithmetic.
+ */
+int dco_top_h_mass(const float* logits_sorted, int n, int h, float alpha, float* mass_out) {
+    if (h == 0 || h > n) return 0;
+    if (alpha <= 1.0f) return 0;
+    float mx = logits_sorted[0];
+    for (int i = 1; i < h; i++) if (logits_sorted[i] > mx) mx = logits_sorted[i];
+    float head = 0.0f;
+    for (int i = 0; i < h; i++) head += expf(logits_sorted[i] - mx);
+    float vh = expf(logits_sorted[h - 1] - mx);
+    float tail = vh * (float)h / (alpha - 1.0f);
+    float denom = head + tail;
+    if (denom <= 0.0f) return 0;
+    *mass_out = head / denom;
+    return 1;
+}
+
+/*
+ * k_check_early_stoppable (nsw.rs:285-300) on the h best ranking keys (ascending dist):
+ * logit = (65536 - dist) / sqrt(dim), fit from rank 5, stoppable iff mass >= threshold.
+ * alpha_out / mass_out (may be NULL) receive the intermediate values (NaN where undefined).
+ */
+int dco_k_check(const uint32_t* dist_bits_sorted, int h, int dim, float threshold, float* alpha_out, float* mass_out) {
+    float* z = (float*)malloc(sizeof(float) * (size_t)(h > 0 ? h : 1));
+    float sq = sqrtf((float)dim);
+    for (int i = 0; i < h; i++) z[i] = (65536.0f - bits_f32(dist_bits_sorted[i])) / sq;
+    float alpha = NAN, mass = NAN;
+    int ok = dco_fit_alpha(z, h, 5, &alpha);
+    if (ok) ok = dco_top_h_mass(z, h, h, alpha, &mass);
+    if (alpha_out) *alpha_out = alpha;
+    if (mass_out) *mass_out = mass;
+    free(z);
+    return ok && mass >= threshold;
+}
+
+/*
+ * The budget the reference's search would stop at (nsw.rs:339-376): the first
+ * checkpoint h of k_check_seq (h < k) whose top-h keys pass the k-check; k otherwise.
+ */
+int dco_adaptive_budget(const uint32_t* dist_bits_sorted, int k, int dim, const int* seq, int n_seq, float threshold) {
+    for (int e = 0; e < n_seq; e++) {
+        int h = seq[e];
+        if (h >= k) break;
+        if (dco_k_check(dist_bits_sorted, h, dim, threshold, NULL, NULL)) return h;
+    }
+    return k;
+}

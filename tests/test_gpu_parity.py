@@ -466,6 +466,61 @@ def test_sequence_sharded_step_emulated_on_one_gpu(oracle_lib):
         e.close()
 
 
+def test_adaptive_budget_k_check(lib, oracle_lib):
+    """The k-check epilogue (nsw.rs:198-300,339-376): budgets against the oracle on the engine's own
+    best-first ranking keys, and the fused step attending only over the budgeted rows."""
+    from diffcache_b200 import DiffCacheGPU
+
+    B, Hkv, G, D, n, topk = 1, 4, 4, 128, 6000, 1024
+    P = B * Hkv
+    rng = np.random.default_rng(97)
+    # keys whose score against q = (4, 0, 0, ...) follows a power law in the rank with a per-problem exponent
+    alphas = [3.0, 1.6, 0.6, 2.2]
+    k = torch.zeros((B, Hkv, n, D), dtype=torch.float32)
+    for p, alpha in enumerate(alphas):
+        logit = 9.0 - alpha * np.log(np.arange(1, n + 1)) + rng.normal(0, 0.02, n)
+        k[0, p, torch.from_numpy(rng.permutation(n)), 0] = torch.from_numpy((logit * np.sqrt(D) / 4.0).astype(np.float32))
+    k[..., 1:] = torch.randn(B, Hkv, n, D - 1, generator=torch.Generator().manual_seed(1)) * 0.5
+    k = k.to(torch.bfloat16)
+    v = torch.randn(B, Hkv, n, D, generator=torch.Generator().manual_seed(2)).to(torch.bfloat16)
+    q = torch.zeros((B, Hkv * G, D), dtype=torch.bfloat16)
+    q[..., 0] = 4.0
+    seq, thr = [100, 200, 400, 800], 0.9
+    eng = DiffCacheGPU(B, Hkv * G, Hkv, D, max_ctx_len=n, adaptive_budget=True, k_check_seq=seq, attn_mass_threshold=thr)
+    eng.prefill(util.u16(k), util.u16(v), None)
+    qd = q.cuda()
+    out = torch.empty_like(qd)
+    idx = torch.zeros((B, Hkv, topk), dtype=torch.int32, device="cuda")
+    eng.decode_attend(qd, out, topk, out_idx=idx)
+    eng.check_status()
+    torch.cuda.synchronize()
+    budget = eng.last_budget().reshape(P)
+    gi = idx.cpu().numpy().reshape(P, topk)
+    ku, vu = util.u16(k).reshape(P, n, D), util.u16(v).reshape(P, n, D)
+    qm = oracle_lib.group_mean(util.u16(q).reshape(-1, D), G, 0)
+    want_budgets = []
+    for p in range(P):
+        bits = oracle_lib.score_rows(ku[p], qm[p], 0)[gi[p]]  # oracle keys of the rows the engine selected, best first
+        want_budgets.append(oracle_lib.adaptive_budget(bits, D, seq, thr))
+    assert budget.tolist() == want_budgets
+    assert len(set(want_budgets)) >= 2 and max(want_budgets) == topk and min(want_budgets) <= 200
+    # the stand-alone entry point gives the same budgets
+    sel_bits = _dev(np.stack([oracle_lib.score_rows(ku[p], qm[p], 0)[gi[p]] for p in range(P)]).view(np.int32))
+    ob = torch.zeros(P, dtype=torch.int32, device="cuda")
+    seq_arr = np.asarray(seq, np.int32)
+    assert lib.dc_adaptive_budget(sel_bits.data_ptr(), topk, P, topk, D, seq_arr.ctypes.data, len(seq), thr, ob.data_ptr(),
+                                  _stream()) == 0
+    torch.cuda.synchronize()
+    assert ob.cpu().numpy().tolist() == want_budgets
+    # attention runs over the first `budget` selected rows only
+    for p in range(P):
+        rows = gi[p][:want_budgets[p]]
+        of, _, _ = oracle_lib.attend(ku[p][rows][None], vu[p][rows][None], util.u16(q).reshape(P * G, D)[p * G:(p + 1) * G],
+                                     G, D ** -0.5, 0)
+        util.assert_attention_close(util.u16(out).reshape(P * G, D)[p * G:(p + 1) * G], of, 0, oracle_lib, ATOL, RTOL)
+    eng.close()
+
+
 def test_snapshot_roundtrip(tmp_path, oracle_lib):
     from diffcache_b200 import DiffCacheGPU
 

@@ -130,3 +130,31 @@ def test_pq_definitions(oracle_lib):
     for m in range(M):
         s = (s + lut[0, m, codes[:, m]]).astype(np.float32)
     assert np.array_equal(bits, (np.float32(65536.0) - s).astype(np.float32).view(np.uint32))
+
+
+def test_k_check_against_numpy_fit(oracle_lib):
+    """fit_alpha_from_logits / estimate_top_h_mass (nsw.rs:198-283) restated with numpy."""
+    rng = np.random.default_rng(8)
+    D = 128
+    for alpha_true in (0.7, 1.3, 2.5):
+        ranks = np.arange(1, 1025)
+        z = (6.0 - alpha_true * np.log(ranks) + rng.normal(0, 0.05, ranks.size)).astype(np.float32)
+        z = np.sort(z)[::-1].copy()
+        dist = (np.float32(65536.0) - z * np.float32(np.sqrt(D))).astype(np.float32)
+        zz = ((np.float32(65536.0) - dist) / np.float32(np.sqrt(D))).astype(np.float32)  # what the engine sees
+        for h in (100, 400, 1024):
+            ok, alpha, mass = oracle_lib.k_check(dist.view(np.uint32)[:h], D, 0.9)
+            x = np.log(np.arange(5, h + 1, dtype=np.float64))
+            slope = np.polyfit(x, zz[4:h].astype(np.float64), 1)[0]
+            assert abs(alpha - (-slope)) < 1e-4
+            if -slope > 1.0:
+                head = np.exp(zz[:h].astype(np.float64) - zz[0]).sum()
+                tail = np.exp(float(zz[h - 1]) - float(zz[0])) * h / (-slope - 1.0)
+                assert abs(mass - head / (head + tail)) < 1e-4
+                assert ok == (mass >= 0.9)
+            else:
+                assert not ok
+        seq = [100, 200, 400, 800]
+        got = oracle_lib.adaptive_budget(dist.view(np.uint32), D, seq, 0.9)
+        want = next((h for h in seq if oracle_lib.k_check(dist.view(np.uint32)[:h], D, 0.9)[0]), 1024)
+        assert got == want

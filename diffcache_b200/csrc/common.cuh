@@ -81,6 +81,21 @@ __device__ __forceinline__ uint4 ld_stream16(const void* p) {
     return __ldcs(reinterpret_cast<const uint4*>(p));
 }
 
+// Streaming 32-byte load (sm_100 has 256-bit global loads): half the load instructions and L1/L2
+// requests per byte of a 16-byte load; read-only path, no L1 allocation, evict-first in L2.
+struct Wide32 { uint4 lo, hi; };
+__device__ __forceinline__ Wide32 ld_stream32(const void* p) {
+    unsigned long long a, b, c, d;
+    asm volatile("ld.global.nc.L1::no_allocate.L2::evict_first.v4.b64 {%0,%1,%2,%3}, [%4];\n"
+                 : "=l"(a), "=l"(b), "=l"(c), "=l"(d) : "l"(p));
+    Wide32 w;
+    w.lo = make_uint4(static_cast<uint32_t>(a), static_cast<uint32_t>(a >> 32), static_cast<uint32_t>(b),
+                      static_cast<uint32_t>(b >> 32));
+    w.hi = make_uint4(static_cast<uint32_t>(c), static_cast<uint32_t>(c >> 32), static_cast<uint32_t>(d),
+                      static_cast<uint32_t>(d >> 32));
+    return w;
+}
+
 // Eight query elements [col0, col0+8) of the retrieval query of one problem as fp32.
 // q_mode 0: q already holds the group mean.  q_mode 1: q holds the `group` query heads of
 // the problem back to back; the mean is the fp32 sum in head order times 1/group, rounded

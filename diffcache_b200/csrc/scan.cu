@@ -94,6 +94,89 @@ score_scan_kernel(const uint16_t* __restrict__ keys, int64_t prob_stride, int64_
     }
 }
 
+
+// Same scan with 32-byte loads: LW = D/16 lanes share a row (16 elements per lane), one warp-wide
+// load covers 32/LW consecutive rows = 1 KB.  Half the load instructions per byte.
+template <int DT, int LW>
+__global__ void __launch_bounds__(kScanThreads)
+score_scan_wide_kernel(const uint16_t* __restrict__ keys, int64_t prob_stride, int64_t n, const uint16_t* __restrict__ q,
+                       int q_mode, int group, uint32_t* __restrict__ scores, int64_t score_stride,
+                       uint32_t* __restrict__ minmax, int rows_per_cta) {
+    constexpr int D = LW * 16;
+    constexpr int R = 32 / LW;
+    constexpr int TR = kLoadsPerTile * R;
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    const int col = lane % LW;
+    const int sub = lane / LW;
+    const int64_t prob = blockIdx.y;
+
+    float qv[16];
+    {
+        float a[8], b[8];
+        load_query8<DT>(q, prob, D, q_mode, group, col * 16, a);
+        load_query8<DT>(q, prob, D, q_mode, group, col * 16 + 8, b);
+#pragma unroll
+        for (int j = 0; j < 8; j++) { qv[j] = a[j]; qv[8 + j] = b[j]; }
+    }
+    const uint16_t* kp = keys + prob * prob_stride + col * 16;
+    uint32_t* sp = scores + prob * score_stride;
+    const int64_t row0 = static_cast<int64_t>(blockIdx.x) * rows_per_cta;
+    const int64_t row_end = min(n, row0 + rows_per_cta);
+    const int my_i = treduce_base<kLoadsPerTile, LW>(lane);
+    const bool writer = (col & ((1 << treduce_plain_bits<kLoadsPerTile, LW>()) - 1)) == 0;
+    uint32_t lo = 0xFFFFFFFFu, hi = 0u;
+
+    for (int64_t tile = row0 + warp * TR; tile < row_end; tile += kScanWarps * TR) {
+        Wide32 w[kLoadsPerTile];
+        if (tile + TR <= row_end) {
+#pragma unroll
+            for (int i = 0; i < kLoadsPerTile; i++) w[i] = ld_stream32(kp + (tile + i * R + sub) * D);
+        } else {
+#pragma unroll
+            for (int i = 0; i < kLoadsPerTile; i++) w[i] = ld_stream32(kp + min(tile + i * R + sub, row_end - 1) * D);
+        }
+        float part[kLoadsPerTile];
+#pragma unroll
+        for (int i = 0; i < kLoadsPerTile; i++) {
+            float f[8], g[8];
+            unpack8<DT>(w[i].lo, f);
+            unpack8<DT>(w[i].hi, g);
+            float a = f[0] * qv[0];
+#pragma unroll
+            for (int j = 1; j < 8; j++) a = fmaf(f[j], qv[j], a);
+#pragma unroll
+            for (int j = 0; j < 8; j++) a = fmaf(g[j], qv[8 + j], a);
+            part[i] = a;
+        }
+        treduce<kLoadsPerTile, LW>(part, lane);
+        constexpr int CNT = treduce_count<kLoadsPerTile, LW>();
+#pragma unroll
+        for (int c = 0; c < CNT; c++) {
+            const int64_t r = tile + (my_i + c) * R + sub;
+            if (writer && r < row_end) {
+                uint32_t b = dist_bits(part[c]);
+                sp[r] = b;
+                lo = min(lo, b);
+                hi = max(hi, b);
+            }
+        }
+    }
+    if (minmax != nullptr) {
+        __shared__ uint32_t s_lo, s_hi;
+        if (threadIdx.x == 0) { s_lo = 0xFFFFFFFFu; s_hi = 0u; }
+        __syncthreads();
+        lo = __reduce_min_sync(0xFFFFFFFFu, lo);
+        hi = __reduce_max_sync(0xFFFFFFFFu, hi);
+        if (lane == 0) { atomicMin(&s_lo, lo); atomicMax(&s_hi, hi); }
+        __syncthreads();
+        if (threadIdx.x == 0 && s_lo <= s_hi) {
+            atomicMin(&minmax[2 * prob], s_lo);
+            atomicMax(&minmax[2 * prob + 1], s_hi);
+        }
+    }
+}
+
 int env_int(const char* name, int dflt) {
     const char* s = std::getenv(name);
     if (s == nullptr || *s == 0) return dflt;
@@ -108,6 +191,15 @@ int launch_scan(const void* keys, int64_t prob_stride, int n_prob, int64_t n, co
     int rows_per_cta = ((rows_cfg + kScanWarps * TR - 1) / (kScanWarps * TR)) * (kScanWarps * TR);
     int64_t chunks = (n + rows_per_cta - 1) / rows_per_cta;
     dim3 grid(static_cast<unsigned>(chunks), static_cast<unsigned>(n_prob));
+    static int wide = env_int("DC_SCAN_WIDE", 1);
+    if (wide && LPR >= 8 && prob_stride % 16 == 0 && (reinterpret_cast<uintptr_t>(keys) & 31) == 0) {
+        // rows_per_cta is a multiple of 8 warps x 8 loads x (32 / (LPR/2)) rows as well (LPR >= 8)
+        score_scan_wide_kernel<DT, LPR / 2><<<grid, kScanThreads, 0, stream>>>(
+            static_cast<const uint16_t*>(keys), prob_stride, n, static_cast<const uint16_t*>(q), q_mode, group, scores,
+            score_stride, minmax, rows_per_cta);
+        DC_CUDA_TRY(cudaGetLastError());
+        return DC_OK;
+    }
     score_scan_kernel<DT, LPR><<<grid, kScanThreads, 0, stream>>>(
         static_cast<const uint16_t*>(keys), prob_stride, n, static_cast<const uint16_t*>(q), q_mode, group, scores,
         score_stride, minmax, rows_per_cta);

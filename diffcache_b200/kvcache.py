@@ -48,6 +48,7 @@ class DiffCache:
         r_sq: Optional[List[List[float]]] = None,
         dtype: str = "bf16",
         device: Optional[int] = None,
+        adaptive_budget: bool = False,
     ) -> None:
         self.num_layers = num_layers
         self.batch_size = batch_size
@@ -90,6 +91,7 @@ class DiffCache:
                 attn_mass_threshold=attn_mass_threshold,
                 k_check_seq=k_check_seq if k_check_seq is not None else [1048576],
                 use_bruteforce=True,
+                adaptive_budget=adaptive_budget,
                 dtype=dtype,
                 device=self.device.index,
             )

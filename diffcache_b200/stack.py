@@ -29,9 +29,12 @@ from .sharded import shard_heads
 class AttentionStack:
     def __init__(self, n_layers: int, hidden: int, batch: int, q_heads: int, kv_heads: int, head_dim: int,
                  context: int, topk: int, sink: int, window: int, dtype: str = "bf16", seed: int = 2000,
-                 device: Optional[torch.device] = None, group: Optional["dist.ProcessGroup"] = None):
-        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
-        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+                 device: Optional[torch.device] = None, group: Optional["dist.ProcessGroup"] = None,
+                 unsharded: bool = False):
+        """``unsharded=True`` builds the whole stack on this device even inside a process group."""
+        use_dist = dist.is_initialized() and not unsharded
+        self.world = dist.get_world_size(group) if use_dist else 1
+        self.rank = dist.get_rank(group) if use_dist else 0
         self.pg = group
         self.device = device or torch.device("cuda", torch.cuda.current_device())
         self.n_layers, self.hidden, self.batch = n_layers, hidden, batch

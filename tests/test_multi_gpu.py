@@ -71,6 +71,48 @@ def _rank_main(rank, world, port, tmpdir):
         dist.destroy_process_group()
 
 
+def _stack_rank_main(rank, world, port, tmpdir):
+    import torch.distributed as dist
+
+    from diffcache_b200.stack import AttentionStack
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        kw = dict(n_layers=3, hidden=512, batch=2, q_heads=16, kv_heads=4, head_dim=128, context=6000, topk=512, sink=16,
+                  window=48, dtype="bf16", seed=77, device=torch.device("cuda", rank))
+        sharded_stack = AttentionStack(**kw)                       # kv heads split over the two ranks
+        x = torch.randn((2, 512), generator=torch.Generator().manual_seed(3)).to(torch.bfloat16).cuda()
+        y = sharded_stack.step(x).clone()
+        for e in sharded_stack.engines:
+            e.check_status()
+        torch.cuda.synchronize()
+        if rank == 0:  # the same stack on one GPU: world of one
+            solo = AttentionStack(unsharded=True, **kw)
+            want = solo.step(x)
+            torch.cuda.synchronize()
+            assert torch.allclose(y.float(), want.float(), rtol=2e-2, atol=2e-2), (y.float() - want.float()).abs().max()
+            solo.close()
+        sharded_stack.close()
+        dist.barrier()
+        open(os.path.join(tmpdir, f"stack_ok{rank}"), "w").write("ok")
+    finally:
+        dist.destroy_process_group()
+
+
+def test_head_sharded_stack_on_two_gpus(tmp_path):
+    """Configuration-2 shape in small: the kv-head-sharded attention stack on two GPUs (one all-gather of
+    the attention output per layer) against the same stack on one GPU."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+
+    port = _free_port()
+    mp.spawn(_stack_rank_main, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    assert (tmp_path / "stack_ok0").exists() and (tmp_path / "stack_ok1").exists()
+
+
 def test_sequence_sharded_step_on_two_gpus(tmp_path):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")

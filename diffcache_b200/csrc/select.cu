@@ -39,6 +39,7 @@ struct SelCtl {
     uint32_t need;        // how many keys are still to be taken from [lo, hi]
     uint32_t t, below, cnt;
     uint32_t out_count, cand_count, dup_count;
+    uint32_t raw_count;   // CTA-local: scores kept by the single-pass path
     uint32_t mn, mx;
     uint32_t max_seg;     // largest first-pass bin below the threshold bin
     uint32_t error;
@@ -129,11 +130,12 @@ __device__ __forceinline__ void for_each_score(const uint32_t* __restrict__ pb, 
 }
 
 // grid = (cluster_size, n_prob), cluster = (cluster_size, 1, 1).
-// dynamic shared memory: out[kpad] u64 | cand[kCandCap] u64 | hist[kBins] u32 | cum[kBins] u32
+// dynamic shared memory: out[kpad] u64 | cand[kCandCap] u64 | hist[kBins] u32 | cum[kBins] u32 | raw[raw_cap] u64
 __global__ void __launch_bounds__(kSelThreads, 1)
 topk_select_kernel(const uint32_t* __restrict__ bits, const uint32_t* __restrict__ ids, int64_t in_stride, int64_t n,
                    int k, const uint32_t* __restrict__ minmax, uint32_t id_offset, uint32_t* __restrict__ out_bits,
-                   uint32_t* __restrict__ out_ids, int64_t out_stride, int kpad, uint32_t* __restrict__ status) {
+                   uint32_t* __restrict__ out_ids, int64_t out_stride, int kpad, int raw_cap,
+                   uint32_t* __restrict__ status) {
     cg::cluster_group cluster = cg::this_cluster();
     const unsigned rank = cluster.block_rank();
     const unsigned csize = cluster.num_blocks();
@@ -145,6 +147,7 @@ topk_select_kernel(const uint32_t* __restrict__ bits, const uint32_t* __restrict
     unsigned long long* s_cand = s_out + kpad;
     uint32_t* s_hist = reinterpret_cast<uint32_t*>(s_cand + kCandCap);
     uint32_t* s_cum = s_hist + kBins;  // exclusive prefix of the first-pass histogram
+    unsigned long long* s_raw = reinterpret_cast<unsigned long long*>(s_cum + kBins);  // (bits, position) pairs
     __shared__ SelCtl ctl;
     __shared__ uint32_t s_warp[32];
     __shared__ uint32_t s_total;
@@ -168,7 +171,7 @@ topk_select_kernel(const uint32_t* __restrict__ bits, const uint32_t* __restrict
     const int k_eff = static_cast<int>(min(static_cast<int64_t>(k), n));
 
     if (tid == 0) {
-        ctl.out_count = 0; ctl.cand_count = 0; ctl.dup_count = 0; ctl.error = 0;
+        ctl.out_count = 0; ctl.cand_count = 0; ctl.dup_count = 0; ctl.raw_count = 0; ctl.error = 0;
         ctl.mn = 0xFFFFFFFFu; ctl.mx = 0u; ctl.max_seg = 0;
     }
     __syncthreads();
@@ -185,6 +188,43 @@ topk_select_kernel(const uint32_t* __restrict__ bits, const uint32_t* __restrict
         const uint32_t id = pi ? pi[i] : i;
         return (static_cast<unsigned long long>(b) << 32) | id;
     };
+
+    // Leader only: locate the bin that holds the `need`-th smallest key of the merged histogram
+    // (ctl.t, ctl.below, ctl.cnt).  On the first pass also keep where each bin starts in sorted order
+    // (s_cum), note the largest bin wholly below the threshold (ctl.max_seg) and recycle the
+    // histogram as per-bin fill counters.
+    auto leader_find_threshold = [&](bool first_pass) {
+        uint32_t h[4], s = 0;  // each thread owns kBins / kSelThreads = 4 consecutive bins
+#pragma unroll
+        for (int u = 0; u < 4; u++) { h[u] = s_hist[tid * 4 + u]; s += h[u]; }
+        uint32_t ex = block_exclusive_scan(s, s_warp, &s_total);
+        if (ex < need && need <= ex + s) {
+            uint32_t run = ex;
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                if (run < need && need <= run + h[u]) { ctl.t = tid * 4 + u; ctl.below = run; ctl.cnt = h[u]; }
+                run += h[u];
+            }
+        }
+        if (tid == 0 && s_total < need) ctl.error = 1;  // cannot happen for consistent inputs
+        if (first_pass) {
+            uint32_t run = ex;
+#pragma unroll
+            for (int u = 0; u < 4; u++) { s_cum[tid * 4 + u] = run; run += h[u]; }
+            __syncthreads();  // ctl.t visible
+            const uint32_t tt = ctl.t;
+            uint32_t mseg = 0;
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                if (static_cast<uint32_t>(tid * 4 + u) < tt) mseg = max(mseg, h[u]);
+                s_hist[tid * 4 + u] = 0;
+            }
+            mseg = __reduce_max_sync(0xFFFFFFFFu, mseg);
+            if ((tid & 31) == 0 && mseg) atomicMax(&ctl.max_seg, mseg);
+        }
+    };
+
+    bool listed = false;  // the single-pass path kept every possible winner in s_raw: no final scan needed
 
     if (!take_all) {
         // ---- key range ----
@@ -205,8 +245,141 @@ topk_select_kernel(const uint32_t* __restrict__ bits, const uint32_t* __restrict
         lo = static_cast<unsigned long long>(mn) << 32;
         hi = (static_cast<unsigned long long>(mx) << 32) | 0xFFFFFFFFull;
 
+        // ---- single-pass path (one CTA per problem) ----
+        // A 1/8 sample of the scores gives a bin U that almost surely lies above the k-th smallest key.
+        // One full pass then histograms only bins <= U and keeps those scores in shared memory, so the
+        // exact threshold bin and all winners come out of ONE read of the score array.  If the sample
+        // misleads (fewer than k keys kept, or more than fit) the general two-pass path below runs.
+        if (csize == 1 && raw_cap > 0) {
+            const unsigned long long range0 = hi - lo;
+            const int width0 = range0 == 0 ? 0 : 64 - __clzll(static_cast<long long>(range0));
+            const int shift0 = max(0, width0 - kBinsLog2);
+            const uint32_t lo32 = static_cast<uint32_t>(lo >> 32);
+            const uint32_t span = static_cast<uint32_t>(hi >> 32) - lo32;
+            const uint32_t* p0 = pb + begin;
+            const uint32_t n0 = static_cast<uint32_t>(end - begin);
+            if (shift0 >= 32 && n0 >= 64u * 1024u) {
+                const int sh = shift0 - 32;
+                for (int b = tid; b < kBins; b += kSelThreads) s_hist[b] = 0;
+                __syncthreads();
+                if ((reinterpret_cast<uintptr_t>(p0) & 15) == 0) {
+                    const uint4* pv = reinterpret_cast<const uint4*>(p0);
+                    for (uint32_t v = tid * 8u; v < (n0 >> 2); v += kSelThreads * 8u) {
+                        const uint4 w = pv[v];
+                        atomicAdd(&s_hist[(w.x - lo32) >> sh], 1u); atomicAdd(&s_hist[(w.y - lo32) >> sh], 1u);
+                        atomicAdd(&s_hist[(w.z - lo32) >> sh], 1u); atomicAdd(&s_hist[(w.w - lo32) >> sh], 1u);
+                    }
+                } else {
+                    for (uint32_t i = tid * 8u; i < n0; i += kSelThreads * 8u) atomicAdd(&s_hist[(p0[i] - lo32) >> sh], 1u);
+                }
+                __syncthreads();
+                {   // U = first bin where the sample count reaches k/8 plus four standard deviations
+                    const float mean = static_cast<float>(k_eff) * 0.125f;
+                    const uint32_t target = static_cast<uint32_t>(mean + 4.0f * sqrtf(mean) + 8.0f);
+                    uint32_t h[4], sum = 0;
+#pragma unroll
+                    for (int u = 0; u < 4; u++) { h[u] = s_hist[tid * 4 + u]; sum += h[u]; }
+                    const uint32_t ex = block_exclusive_scan(sum, s_warp, &s_total);
+                    if (tid == 0) ctl.t = kBins - 1;
+                    __syncthreads();
+                    if (ex < target && target <= ex + sum) {
+                        uint32_t run = ex;
+#pragma unroll
+                        for (int u = 0; u < 4; u++) {
+                            if (run < target && target <= run + h[u]) ctl.t = tid * 4 + u;
+                            run += h[u];
+                        }
+                    }
+                    __syncthreads();
+                }
+                const uint32_t U = ctl.t;
+                for (int b = tid; b < kBins; b += kSelThreads) s_hist[b] = 0;
+                __syncthreads();
+                // Survivors (bin <= U, ~1.3 k of n) go to the shared list without any atomic that returns a
+                // value in the loop: a warp fills private 32-slot chunks of the list (positions by ballot and
+                // popcount) and only fetches a new chunk from the shared counter when the current one is full;
+                // unused slots keep the 0xFF..F sentinel the list was filled with.
+                for (int r = tid; r < raw_cap; r += kSelThreads) s_raw[r] = ~0ull;
+                __syncthreads();
+                {
+                    const uint32_t lane = tid & 31;
+                    const uint32_t lt = (1u << lane) - 1u;
+                    uint32_t chunk_base = 0, chunk_fill = 32;  // "full": the first survivor fetches a chunk
+                    auto keep_one = [&](bool valid, uint32_t b, uint32_t i) {
+                        const uint32_t d = b - lo32;
+                        const uint32_t bin = d >> sh;
+                        const bool keep = valid && d <= span && bin <= U;
+                        const unsigned mask = __ballot_sync(0xFFFFFFFFu, keep);
+                        if (mask == 0) return;
+                        const uint32_t cnt = __popc(mask);
+                        if (chunk_fill + cnt > 32) {  // warp-uniform
+                            uint32_t nb = 0;
+                            if (lane == 0) nb = atomicAdd(&ctl.raw_count, 32u);
+                            chunk_base = __shfl_sync(0xFFFFFFFFu, nb, 0);
+                            chunk_fill = 0;
+                        }
+                        if (keep) {
+                            atomicAdd(&s_hist[bin], 1u);
+                            const uint32_t pos = chunk_base + chunk_fill + __popc(mask & lt);
+                            if (pos < static_cast<uint32_t>(raw_cap)) s_raw[pos] = (static_cast<unsigned long long>(b) << 32) | i;
+                        }
+                        chunk_fill += cnt;
+                    };
+                    const uint32_t first = static_cast<uint32_t>(begin);
+                    uint32_t done = 0;
+                    if ((reinterpret_cast<uintptr_t>(p0) & 15) == 0) {
+                        const uint32_t nvec = n0 >> 2;
+                        const uint4* pv = reinterpret_cast<const uint4*>(p0);
+                        for (uint32_t v0 = 0; v0 < nvec; v0 += kSelThreads * kSelUnroll) {  // bounds are warp-uniform
+                            uint4 w[kSelUnroll];
+#pragma unroll
+                            for (int u = 0; u < kSelUnroll; u++) {
+                                const uint32_t v = v0 + u * kSelThreads + tid;
+                                w[u] = v < nvec ? pv[v] : make_uint4(0, 0, 0, 0);
+                            }
+#pragma unroll
+                            for (int u = 0; u < kSelUnroll; u++) {
+                                const uint32_t v = v0 + u * kSelThreads + tid;
+                                const bool valid = v < nvec;
+                                const uint32_t i = first + 4 * v;
+                                keep_one(valid, w[u].x, i); keep_one(valid, w[u].y, i + 1);
+                                keep_one(valid, w[u].z, i + 2); keep_one(valid, w[u].w, i + 3);
+                            }
+                        }
+                        done = nvec << 2;
+                    }
+                    for (uint32_t i0 = done; i0 < n0; i0 += kSelThreads) {
+                        const uint32_t i = i0 + tid;
+                        const bool valid = i < n0;
+                        keep_one(valid, valid ? p0[i] : 0u, first + i);
+                    }
+                }
+                __syncthreads();
+                bool ok = ctl.raw_count <= static_cast<uint32_t>(raw_cap);  // list extent incl. unused slots
+                if (ok) {
+                    leader_find_threshold(true);  // flags ctl.error = 1 when fewer than `need` keys were kept
+                    __syncthreads();
+                    ok = ctl.error == 0 && ctl.cnt <= kCandCap;
+                    if (ok) {
+                        need -= ctl.below;
+                        const unsigned long long nlo = lo + (static_cast<unsigned long long>(ctl.t) << shift0);
+                        const unsigned long long sp = (1ull << shift0) - 1ull;
+                        hi = (nlo + sp < nlo) ? hi : min(hi, nlo + sp);
+                        lo = nlo;
+                        passes = 1; first_bits_only = true; bin_lo32 = lo32; bin_sh = sh;
+                        listed = true;
+                    }
+                }
+                if (!listed) {  // start over on the general path with clean state
+                    __syncthreads();
+                    if (tid == 0) { ctl.raw_count = 0; ctl.max_seg = 0; ctl.error = 0; }
+                    __syncthreads();
+                }
+            }
+        }
+
         // ---- narrowing passes ----
-        for (int pass = 0; pass < kMaxPasses; pass++) {
+        for (int pass = 0; pass < kMaxPasses && !listed; pass++) {
             const unsigned long long range = hi - lo;
             const int width = range == 0 ? 0 : 64 - __clzll(static_cast<long long>(range));
             const int shift = max(0, width - kBinsLog2);
@@ -244,39 +417,7 @@ topk_select_kernel(const uint32_t* __restrict__ bits, const uint32_t* __restrict
             }
             cluster.sync();  // merged histogram complete in the leader
 
-            if (rank == 0) {
-                // each thread owns kBins / kSelThreads = 4 consecutive bins
-                uint32_t h[4], s = 0;
-#pragma unroll
-                for (int u = 0; u < 4; u++) { h[u] = s_hist[tid * 4 + u]; s += h[u]; }
-                uint32_t ex = block_exclusive_scan(s, s_warp, &s_total);
-                if (ex < need && need <= ex + s) {
-                    uint32_t run = ex;
-#pragma unroll
-                    for (int u = 0; u < 4; u++) {
-                        if (run < need && need <= run + h[u]) { ctl.t = tid * 4 + u; ctl.below = run; ctl.cnt = h[u]; }
-                        run += h[u];
-                    }
-                }
-                if (tid == 0 && s_total < need) ctl.error = 1;  // cannot happen for consistent inputs
-                if (pass == 0) {
-                    // Keep where each bin starts in sorted order, note the largest bin that lies wholly
-                    // below the threshold, and recycle the histogram as per-bin fill counters.
-                    uint32_t run = ex;
-#pragma unroll
-                    for (int u = 0; u < 4; u++) { s_cum[tid * 4 + u] = run; run += h[u]; }
-                    __syncthreads();  // ctl.t visible
-                    const uint32_t tt = ctl.t;
-                    uint32_t mseg = 0;
-#pragma unroll
-                    for (int u = 0; u < 4; u++) {
-                        if (static_cast<uint32_t>(tid * 4 + u) < tt) mseg = max(mseg, h[u]);
-                        s_hist[tid * 4 + u] = 0;
-                    }
-                    mseg = __reduce_max_sync(0xFFFFFFFFu, mseg);
-                    if ((tid & 31) == 0 && mseg) atomicMax(&ctl.max_seg, mseg);
-                }
-            }
+            if (rank == 0) leader_find_threshold(pass == 0);
             cluster.sync();  // ctl published
             const uint32_t t = l_ctl->t, below = l_ctl->below, cnt = l_ctl->cnt;
             need -= below;
@@ -306,8 +447,7 @@ topk_select_kernel(const uint32_t* __restrict__ bits, const uint32_t* __restrict
         // Winners are ~k of n scores, so a 32-bit pre-test on the dist bits rejects almost every
         // element before its id is looked at; positions come from one shared-memory atomic each.
         const uint32_t hi32 = static_cast<uint32_t>(hi >> 32);
-        for_each_score(pb, begin, end, [&](uint32_t b, uint32_t i) {
-            if (b > hi32) return;
+        auto place = [&](uint32_t b, uint32_t i) {
             const unsigned long long key = key_of(b, i);
             if (key < lo) {
                 uint32_t pos;
@@ -327,7 +467,19 @@ topk_select_kernel(const uint32_t* __restrict__ bits, const uint32_t* __restrict
                     if (pos < kCandCap) l_cand[pos] = key;
                 }
             }
-        });
+        };
+        if (listed) {  // every key up to the threshold bin is already in shared memory
+            const uint32_t extent = ctl.raw_count;
+            for (uint32_t r = tid; r < extent; r += kSelThreads) {
+                const unsigned long long e = s_raw[r];
+                if (e != ~0ull) place(static_cast<uint32_t>(e >> 32), static_cast<uint32_t>(e & 0xFFFFFFFFull));
+            }
+        } else {
+            for_each_score(pb, begin, end, [&](uint32_t b, uint32_t i) {
+                if (b > hi32) return;
+                place(b, i);
+            });
+        }
     }
     cluster.sync();  // all remote writes into the leader have landed
     if (rank != 0) return;
@@ -417,6 +569,10 @@ int topk_select(const uint32_t* bits, const uint32_t* ids, int64_t in_stride, in
     int kpad = 1;
     while (kpad < k) kpad <<= 1;
     size_t smem = static_cast<size_t>(kpad) * 8 + static_cast<size_t>(kCandCap) * 8 + 2 * kBins * 4;
+    // scores kept by the single-pass path: room for every winner, a full threshold bin and the sampling slack
+    int raw_cap = 2 * kpad + kCandCap;
+    if (smem + static_cast<size_t>(raw_cap) * 8 > 200 * 1024) raw_cap = 0;
+    smem += static_cast<size_t>(raw_cap) * 8;
 
     // Enough CTAs per problem to occupy the SMs, at most the portable cluster size of 8,
     // and no more than one CTA per 16K keys.
@@ -439,7 +595,7 @@ int topk_select(const uint32_t* bits, const uint32_t* ids, int64_t in_stride, in
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     DC_CUDA_TRY(cudaLaunchKernelEx(&cfg, topk_select_kernel, bits, ids, in_stride, n, k, minmax, id_offset, out_bits,
-                                   out_ids, out_stride, kpad, status));
+                                   out_ids, out_stride, kpad, raw_cap, status));
     return DC_OK;
 }
 

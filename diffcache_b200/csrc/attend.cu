@@ -75,13 +75,11 @@ __device__ __forceinline__ void mma_16816(float& d0, float& d1, uint32_t a0, uin
     }
 }
 
-__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* smem_row) {
-    const unsigned addr = static_cast<unsigned>(__cvta_generic_to_shared(smem_row));
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], unsigned addr) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
 }
-__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* smem_row) {
-    const unsigned addr = static_cast<unsigned>(__cvta_generic_to_shared(smem_row));
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], unsigned addr) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
 }
@@ -194,13 +192,12 @@ sparse_attend_kernel(const AttendArgs a) {
             reinterpret_cast<const uint4*>(a.v_new + prob * D)[tid];
     }
 
-    // Row ids of this lane's NCOPY rows of tile `t` (0xFFFFFFFF where the slot is not a store row).
-    auto fetch_ids = [&](int t, uint32_t (&ids)[NCOPY]) {
-#pragma unroll
-        for (int i = 0; i < NCOPY; i++) {
-            const int j = j0 + t * TILE + warp * RW + i * R + sub;
-            ids[i] = (t < n_tiles && j < j1 && j < n_sel_eff) ? selp[j] : 0xFFFFFFFFu;
-        }
+    // Row id of ONE of the NCOPY rows this lane group copies in tile `t`: lane `col` (< NCOPY) of a group
+    // holds the id of row i = col; the copy loop fetches it with a shuffle (0xFFFFFFFF where the slot is
+    // not a store row).  One global load per lane and tile instead of NCOPY.
+    auto fetch_id = [&](int t) -> uint32_t {
+        const int j = j0 + t * TILE + warp * RW + col * R + sub;
+        return (col < NCOPY && t < n_tiles && j < j1 && j < n_sel_eff) ? selp[j] : 0xFFFFFFFFu;
     };
     // Issue the copies of tile `t` into its ring slot (one commit group per call, possibly empty).
     // Fast path: every row of the tile is a selected store row, so a row address is one multiply-add
@@ -210,7 +207,7 @@ sparse_attend_kernel(const AttendArgs a) {
     for (int i = 0; i < NCOPY; i++) soff[i] = swz<D>(warp * RW + i * R + sub, col);
     const uint16_t* kst_col = kst + col * 8;
     const int64_t v_minus_k = vst - kst;  // elements
-    auto issue_tile = [&](int t, const uint32_t (&ids)[NCOPY]) {
+    auto issue_tile = [&](int t, uint32_t my_id) {
         if (t < n_tiles) {
             unsigned char* ks = att_smem + (t % NS) * STAGE_BYTES;
             unsigned char* vs = ks + TILE * D * 2;
@@ -218,7 +215,8 @@ sparse_attend_kernel(const AttendArgs a) {
             if (jt + TILE <= min(j1, a.n_sel)) {
 #pragma unroll
                 for (int i = 0; i < NCOPY; i++) {
-                    const int64_t row = static_cast<int64_t>(ids[i]) - a.sel_base;
+                    const uint32_t id = __shfl_sync(0xFFFFFFFFu, my_id, sub * LPR + i);
+                    const int64_t row = static_cast<int64_t>(id) - a.sel_base;
                     const bool ok = row >= 0 && row < a.n_rows;  // ids of other shards and pads are skipped
                     const uint16_t* kp = ok ? kst_col + row * D : a.q;
                     cp_async16(ks + soff[i], kp, ok ? 16 : 0);
@@ -243,9 +241,10 @@ sparse_attend_kernel(const AttendArgs a) {
                     const int j = jt + r;
                     const uint16_t* kp = nullptr;
                     const uint16_t* vp = nullptr;
+                    const uint32_t id = __shfl_sync(0xFFFFFFFFu, my_id, sub * LPR + i);
                     if (j < j1) {
                         if (j < a.n_sel) {
-                            const int64_t row = static_cast<int64_t>(ids[i]) - a.sel_base;
+                            const int64_t row = static_cast<int64_t>(id) - a.sel_base;
                             if (row >= 0 && row < a.n_rows) { kp = kst + row * D; vp = vst + row * D; }
                         } else if (j < a.n_sel + a.res_len) {
                             const int64_t row = j - a.n_sel;
@@ -272,43 +271,65 @@ sparse_attend_kernel(const AttendArgs a) {
 #pragma unroll
     for (int nt = 0; nt < NT; nt++) { o_acc[nt][0] = 0.0f; o_acc[nt][1] = 0.0f; }
 
-    uint32_t ids[NCOPY];
+    uint32_t my_id;
 #pragma unroll
     for (int t = 0; t < NS - 1; t++) {  // prologue: tiles 0 .. NS-2
-        fetch_ids(t, ids);
-        issue_tile(t, ids);
+        my_id = fetch_id(t);
+        issue_tile(t, my_id);
     }
-    fetch_ids(NS - 1, ids);
+    my_id = fetch_id(NS - 1);
+
+    // ldmatrix addresses: 32-bit shared addresses, lane-dependent parts computed once.  A chunk index c
+    // XORed with (row & 7) = (lane & 7) splits into a part that depends on the k-step / output tile
+    // (compile-time constant XOR a lane constant) and a low part that is a lane constant.
+    const unsigned smem_base = smem_u32(att_smem);
+    const unsigned x7 = lane & 7;
+    const unsigned lane_row_qk = (warp * RW + x7) * (D * 2);                               // + (rb*16 + grp*8) rows
+    const unsigned lane_row_pv = (warp * RW + ((lane >> 3) & 1) * 8 + x7) * (D * 2);       // + rb*16 rows
+    const unsigned xq = (x7 & 4u) << 4, lowq = (((lane >> 3) ^ x7) & 3u) << 4;             // chunk = 4*kk + (lane>>3)
+    const unsigned xp = (x7 & 6u) << 4, lowp = (((lane >> 4) ^ x7) & 1u) << 4;             // chunk = 2*n2 + (lane>>4)
 
     for (int t = 0; t < n_tiles; t++) {
         __syncthreads();  // tile t-1 fully consumed: its ring slot may be overwritten
-        issue_tile(t + NS - 1, ids);
-        fetch_ids(t + NS, ids);
+        issue_tile(t + NS - 1, my_id);
+        my_id = fetch_id(t + NS);
         cp_async_wait<NS - 1>();
         __syncthreads();  // every thread's copies of tile t have landed
 
-        const unsigned char* ks = att_smem + (t % NS) * STAGE_BYTES;
-        const unsigned char* vs = ks + TILE * D * 2;
+        const unsigned ks = smem_base + (t % NS) * STAGE_BYTES;
+        const unsigned vs = ks + TILE * D * 2;
         const unsigned char* valid = s_valid[t % NS];
 
 #pragma unroll
         for (int rb = 0; rb < RB; rb++) {
             const int row0 = warp * RW + rb * 16;  // this warp's 16 rows
             // ---- S = Q.K^T for two 8-row groups: sc[2*grp + {0,1}] = rows row0 + 8*grp + 2*tq + {0,1} ----
+            // mma.sync has a long issue-to-result latency here, so the k-steps are spread over four
+            // independent accumulator chains (2 groups x even/odd k-step) instead of one chain per group.
             float sc[4];
+            {
+                float acc[2][2][2];
 #pragma unroll
-            for (int grp = 0; grp < 2; grp++) {
-                float c0 = 0.0f, c1 = 0.0f;
+                for (int grp = 0; grp < 2; grp++)
+#pragma unroll
+                    for (int e = 0; e < 2; e++) { acc[grp][e][0] = 0.0f; acc[grp][e][1] = 0.0f; }
 #pragma unroll
                 for (int kk = 0; kk < KSTEPS / 2; kk++) {
-                    uint32_t bk[4];  // B fragments of k-steps 2kk (bk[0], bk[1]) and 2kk+1 (bk[2], bk[3])
-                    ldmatrix_x4(bk, ks + swz<D>(row0 + grp * 8 + (lane & 7), 4 * kk + (lane >> 3)));
-                    mma_16816<DT>(c0, c1, qa[2 * kk][0], qa[2 * kk][1], bk[0], bk[1]);
-                    mma_16816<DT>(c0, c1, qa[2 * kk + 1][0], qa[2 * kk + 1][1], bk[2], bk[3]);
+#pragma unroll
+                    for (int grp = 0; grp < 2; grp++) {
+                        uint32_t bk[4];  // B fragments of k-steps 2kk (bk[0], bk[1]) and 2kk+1 (bk[2], bk[3])
+                        ldmatrix_x4(bk, ks + lane_row_qk + (rb * 16 + grp * 8) * (D * 2) +
+                                            ((static_cast<unsigned>(4 * kk) << 4) ^ xq) + lowq);
+                        mma_16816<DT>(acc[grp][0][0], acc[grp][0][1], qa[2 * kk][0], qa[2 * kk][1], bk[0], bk[1]);
+                        mma_16816<DT>(acc[grp][1][0], acc[grp][1][1], qa[2 * kk + 1][0], qa[2 * kk + 1][1], bk[2], bk[3]);
+                    }
                 }
-                const int r = row0 + grp * 8 + 2 * tq;
-                sc[2 * grp] = valid[r] ? c0 * a.scale_log2 : -INFINITY;
-                sc[2 * grp + 1] = valid[r + 1] ? c1 * a.scale_log2 : -INFINITY;
+#pragma unroll
+                for (int grp = 0; grp < 2; grp++) {
+                    const int r = row0 + grp * 8 + 2 * tq;
+                    sc[2 * grp] = valid[r] ? (acc[grp][0][0] + acc[grp][1][0]) * a.scale_log2 : -INFINITY;
+                    sc[2 * grp + 1] = valid[r + 1] ? (acc[grp][0][1] + acc[grp][1][1]) * a.scale_log2 : -INFINITY;
+                }
             }
             // ---- online softmax over the 16 rows (the 4 lanes of a head hold 4 rows each) ----
             float mx = fmaxf(fmaxf(sc[0], sc[1]), fmaxf(sc[2], sc[3]));
@@ -329,14 +350,27 @@ sparse_attend_kernel(const AttendArgs a) {
             uint32_t p_hi[2], p_lo[2];
             pack_hi_lo<DT>(p[0], p[1], p_hi[0], p_lo[0]);  // rows 2tq, 2tq+1      (k = 2tq, 2tq+1)
             pack_hi_lo<DT>(p[2], p[3], p_hi[1], p_lo[1]);  // rows 8+2tq, 8+2tq+1  (k = 2tq+8, 2tq+9)
+            // Each output tile takes two MMAs (value and residue of P) on the same accumulator; they are
+            // issued four tiles apart so that the second never waits for the first.
 #pragma unroll
-            for (int n2 = 0; n2 < NT / 2; n2++) {
-                uint32_t bv[4];  // V^T fragments: (bv[0], bv[1]) for output tile 2*n2, (bv[2], bv[3]) for 2*n2+1
-                ldmatrix_x4_trans(bv, vs + swz<D>(row0 + ((lane >> 3) & 1) * 8 + (lane & 7), 2 * n2 + (lane >> 4)));
-                mma_16816<DT>(o_acc[2 * n2][0], o_acc[2 * n2][1], p_hi[0], p_hi[1], bv[0], bv[1]);
-                mma_16816<DT>(o_acc[2 * n2][0], o_acc[2 * n2][1], p_lo[0], p_lo[1], bv[0], bv[1]);
-                mma_16816<DT>(o_acc[2 * n2 + 1][0], o_acc[2 * n2 + 1][1], p_hi[0], p_hi[1], bv[2], bv[3]);
-                mma_16816<DT>(o_acc[2 * n2 + 1][0], o_acc[2 * n2 + 1][1], p_lo[0], p_lo[1], bv[2], bv[3]);
+            for (int n4 = 0; n4 < NT / 8; n4++) {
+                uint32_t bv[4][4];  // V^T fragments of 8 output tiles: (bv[j][0], bv[j][1]) tile 2*(4*n4+j), (bv[j][2], bv[j][3]) the next
+#pragma unroll
+                for (int j = 0; j < 4; j++)
+                    ldmatrix_x4_trans(bv[j], vs + lane_row_pv + (rb * 16) * (D * 2) +
+                                                 ((static_cast<unsigned>(2 * (4 * n4 + j)) << 4) ^ xp) + lowp);
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const int n2 = 4 * n4 + j;
+                    mma_16816<DT>(o_acc[2 * n2][0], o_acc[2 * n2][1], p_hi[0], p_hi[1], bv[j][0], bv[j][1]);
+                    mma_16816<DT>(o_acc[2 * n2 + 1][0], o_acc[2 * n2 + 1][1], p_hi[0], p_hi[1], bv[j][2], bv[j][3]);
+                }
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const int n2 = 4 * n4 + j;
+                    mma_16816<DT>(o_acc[2 * n2][0], o_acc[2 * n2][1], p_lo[0], p_lo[1], bv[j][0], bv[j][1]);
+                    mma_16816<DT>(o_acc[2 * n2 + 1][0], o_acc[2 * n2 + 1][1], p_lo[0], p_lo[1], bv[j][2], bv[j][3]);
+                }
             }
         }
     }

@@ -603,10 +603,36 @@ def main():
     for _ in range(3):
         e2e_step()
     barrier()
+    # the same call sequence (copies in, step, copy out) captured once; each step still ends with the
+    # host waiting for its result
+    e2e_call = e2e_step
+    try:
+        ge = torch.cuda.CUDAGraph()
+        es = torch.cuda.Stream()
+        es.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(es):
+            with torch.cuda.graph(ge, stream=es):
+                q_d.copy_(q_h, non_blocking=True)
+                kn_d.copy_(kn_h, non_blocking=True)
+                vn_d.copy_(vn_h, non_blocking=True)
+                eng.decode_attend(q_d, out, cfg.topk, res_k=res_k, res_v=res_v, res_len=res_rows, k_new=kn_d, v_new=vn_d)
+                out_h.copy_(out, non_blocking=True)
+        torch.cuda.current_stream().wait_stream(es)
+
+        def e2e_graph_step():
+            ge.replay()
+            torch.cuda.current_stream().synchronize()
+
+        for _ in range(3):
+            e2e_graph_step()
+        e2e_call = e2e_graph_step
+    except Exception as exc:
+        print(f"# e2e graph capture skipped: {exc}", file=sys.stderr)
+    barrier()
     f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     f0.record()
     for _ in range(args.steps):
-        e2e_step()
+        e2e_call()
     f1.record()
     barrier()
     e2e_ms = f0.elapsed_time(f1)

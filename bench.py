@@ -666,8 +666,8 @@ def main():
                 "frac": scan_gbs / peak, "peak_source": f"MEASURED_PEAKS.json hbm_gbs ({peak_kind})",
                 "frac_of_8tbs_nominal": scan_gbs / 8000.0,
                 # dram__bytes_read.sum + dram__bytes_write.sum of one launch: ncu capture of the 2-sequence case
-                # (534.54 MB + 7.2 MB, profiles/score_scan_cfg1_b2.md) scaled by the 8x rows of this workload
-                "traffic": int(8 * (534.54e6 + 7.2e6)) if cfg.name == "cfg1" else None,
+                # (534.55 MB + 9.54 MB, profiles/score_scan_cfg1_b2.md) scaled by the 8x rows of this workload
+                "traffic": int(8 * (534.55e6 + 9.54e6)) if cfg.name == "cfg1" else None,
                 "algorithmic_bytes_per_launch": cfg.scan_bytes(), "avg_launch_ms": scan_ms,
             },
             "step_roofline": {"achieved": step_gbs, "frac_of_measured": step_gbs / peak,

@@ -468,17 +468,43 @@ lse_combine_kernel(const float* __restrict__ part_acc, int64_t acc_ps, int64_t a
     }
     __syncthreads();
     const float L = s_L;
-    for (int d = tid; d < dim; d += kCombineThreads) {
-        float o = 0.0f;
-        int s = 0;
-        for (; s + 4 <= n_part; s += 4) {  // four independent loads in flight
-            const float a0 = acc[(s + 0) * acc_ps + d], a1 = acc[(s + 1) * acc_ps + d];
-            const float a2 = acc[(s + 2) * acc_ps + d], a3 = acc[(s + 3) * acc_ps + d];
-            o += a0 * s_w[s] + a1 * s_w[s + 1] + a2 * s_w[s + 2] + a3 * s_w[s + 3];
+    const bool vec_ok = (dim % 4 == 0) && (dim / 4 <= kCombineThreads) && (kCombineThreads % (dim / 4) == 0) &&
+                        (acc_ps % 4 == 0) && (acc_rs % 4 == 0) && ((reinterpret_cast<uintptr_t>(part_acc) & 15) == 0);
+    if (vec_ok) {
+        // 16-byte loads; the parts are dealt round-robin to dim/4-lane groups so that their loads are
+        // in flight together, and the groups' sums are added through shared memory
+        __shared__ __align__(16) float s_part[kCombineThreads * 4];
+        const int lanes = dim / 4, groups = kCombineThreads / lanes;
+        const int g = tid / lanes, l = tid % lanes;
+        float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int s = g; s < n_part; s += groups) {
+            const float4 a4 = *reinterpret_cast<const float4*>(acc + s * acc_ps + 4 * l);
+            const float w = s_w[s];
+            o.x += a4.x * w; o.y += a4.y * w; o.z += a4.z * w; o.w += a4.w * w;
         }
-        for (; s < n_part; s++) o += acc[s * acc_ps + d] * s_w[s];
-        if (out) out[row * dim + d] = float_to_elem<DT>(L > 0.0f ? o / L : 0.0f);
-        if (out_acc) out_acc[row * dim + d] = o;
+        *reinterpret_cast<float4*>(&s_part[(g * lanes + l) * 4]) = o;
+        __syncthreads();
+        if (tid < lanes) {
+            float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int gg = 0; gg < groups; gg++) {
+                const float4 p4 = *reinterpret_cast<const float4*>(&s_part[(gg * lanes + tid) * 4]);
+                t.x += p4.x; t.y += p4.y; t.z += p4.z; t.w += p4.w;
+            }
+            const float v4[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const int d = 4 * tid + j;
+                if (out) out[row * dim + d] = float_to_elem<DT>(L > 0.0f ? v4[j] / L : 0.0f);
+                if (out_acc) out_acc[row * dim + d] = v4[j];
+            }
+        }
+    } else {
+        for (int d = tid; d < dim; d += kCombineThreads) {
+            float o = 0.0f;
+            for (int s = 0; s < n_part; s++) o += acc[s * acc_ps + d] * s_w[s];
+            if (out) out[row * dim + d] = float_to_elem<DT>(L > 0.0f ? o / L : 0.0f);
+            if (out_acc) out_acc[row * dim + d] = o;
+        }
     }
     if (tid == 0) {
         if (out_lse) out_lse[row] = L > 0.0f ? (M + log2f(L)) * 0.6931471805599453f : -INFINITY;

@@ -249,7 +249,7 @@ def _run_decode(eng, q, res_k, res_v, res_len, k_new, v_new, topk):
 
 
 @pytest.mark.parametrize("dtype,G,D", [("bf16", 4, 128), ("bf16", 7, 128), ("bf16", 1, 128), ("bf16", 2, 64),
-                                       ("fp16", 4, 128), ("bf16", 8, 256)])
+                                       ("fp16", 4, 128), ("bf16", 8, 256), ("bf16", 16, 128), ("fp16", 3, 64)])
 def test_fused_decode_step_matches_oracle(oracle_lib, dtype, G, D):
     from diffcache_b200 import DiffCacheGPU
 
@@ -327,6 +327,55 @@ def test_sparse_attend_fp32_partials(lib, oracle_lib, G, D, n_sel):
                               _stream()) == 0
     torch.cuda.synchronize()
     util.assert_attention_close(util.u16(out), of, 0, oracle_lib, ATOL, RTOL)
+
+
+def test_fused_step_replayed_from_a_cuda_graph():
+    """The per-step entry points only enqueue work on the given stream (all buffers are allocated at
+    engine creation), so a step can be captured once and replayed — the way the reference drives its
+    decode layers (src/diffcache/base.py:116-155).  The replay must reproduce the eager result exactly
+    and follow new inputs written into the captured buffers."""
+    from diffcache_b200 import DiffCacheGPU
+
+    B, Hkv, G, D, n, topk, res = 2, 2, 4, 128, 20000, 1024, 80
+    k, v, q = util.small_problem(B, Hkv, G, n + res + 1, D, seed=55)
+    eng = DiffCacheGPU(B, Hkv * G, Hkv, D, max_ctx_len=n)
+    eng.prefill(k[:, :, :n].contiguous().cuda().view(torch.uint16), v[:, :, :n].contiguous().cuda().view(torch.uint16))
+    rk = torch.zeros((B, Hkv, res + 8, D), dtype=torch.bfloat16, device="cuda")
+    rv = torch.zeros_like(rk)
+    rk[:, :, :res] = k[:, :, n:n + res].cuda(); rv[:, :, :res] = v[:, :, n:n + res].cuda()
+    kn, vn = k[:, :, -1].contiguous().cuda(), v[:, :, -1].contiguous().cuda()
+    qd = q.cuda()
+    out = torch.empty_like(qd)
+    idx = torch.zeros((B, Hkv, topk), dtype=torch.int32, device="cuda")
+
+    def step():
+        eng.decode_attend(qd, out, topk, res_k=rk, res_v=rv, res_len=res, k_new=kn, v_new=vn, out_idx=idx)
+
+    step()
+    torch.cuda.synchronize()
+    want_out, want_idx = out.clone(), idx.clone()
+    g = torch.cuda.CUDAGraph()
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        with torch.cuda.graph(g, stream=s):
+            step()
+    torch.cuda.current_stream().wait_stream(s)
+    out.zero_(); idx.zero_()
+    g.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(idx, want_idx) and torch.equal(out, want_out)
+    # a new query written into the captured input buffer
+    q2 = (q.float().flip(0) * 0.7).to(torch.bfloat16).cuda()
+    qd.copy_(q2)
+    g.replay()
+    torch.cuda.synchronize()
+    got_out, got_idx = out.clone(), idx.clone()
+    step()
+    torch.cuda.synchronize()
+    assert torch.equal(got_idx, idx) and torch.equal(got_out, out)
+    eng.check_status()
+    eng.close()
 
 
 def test_fused_step_edge_cases(oracle_lib):

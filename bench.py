@@ -662,7 +662,7 @@ def main():
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": cfg.dtype, "data": "synthetic", "config": workload_config(cfg, world),
             "roofline": {
-                "bound": "hbm", "kernel": "score_scan_kernel", "achieved": scan_gbs, "peak": peak, "unit": "GB/s",
+                "bound": "hbm", "kernel": "score_scan_wide_kernel", "achieved": scan_gbs, "peak": peak, "unit": "GB/s",
                 "frac": scan_gbs / peak, "peak_source": f"MEASURED_PEAKS.json hbm_gbs ({peak_kind})",
                 "frac_of_8tbs_nominal": scan_gbs / 8000.0,
                 # dram__bytes_read.sum + dram__bytes_write.sum of one launch: ncu capture of the 2-sequence case

@@ -5,8 +5,12 @@ of the reference engine (diffcache_cpu/src/nsw.rs:592-630,
 diffcache_cpu/src/lib.rs:373-404) plus fp64 attention with the semantics of the
 ``flash_attn_with_kvcache`` call at src/diffcache/base.py:134-142.
 
-Parity unpinned: the reference has no tests or golden vectors for this path;
-only the top-k ordering is pinned (against the DualHeap test sequences).
+Pinned against (1) outputs of the reference's own PyTorch statement of the path (exact branch of
+``gqa_topk_attention``, tools/topk_test.py:303-470; ``tests/golden/spec_vectors.npz``) for the
+chosen rows, their order and the attention output, and (2) the DualHeap test sequences for the
+top-k ordering (``tests/golden/select_kat.json``).  Parity unpinned for the Rust engine's own
+arithmetic: it has no tests or golden vectors for this path and cannot be built here, so the
+last bit of ``dist`` is defined by this oracle (exact dot, rounded once).
 
 Only ``tests/``, ``__graft_entry__.smoke()`` and ``bench.py``'s CPU-baseline /
 reference legs may import this package.

@@ -90,3 +90,74 @@ def assert_attention_close(got_u16, want_f32, dtype, oracle, atol=1e-3, rtol=2e-
     tol = atol + rtol * np.abs(want) + half_ulp
     bad = np.abs(got - want) > tol
     assert not bad.any(), f"{bad.sum()} outputs off; worst {np.max(np.abs(got - want) - tol):.3e} beyond tolerance"
+
+
+# ---- inputs of the functional-spec fixtures (tests/golden/spec_vectors.npz) ----
+# Generated with integer hashing only, so the same bytes come out on every platform, and
+# quantised so that every value is exact in bf16 AND fp16, the group-mean query is exact, and
+# every dot product is exact in fp32 in any summation order.
+
+SPEC_CASES = {
+    # name: batch, kv_heads, group, head_dim, kv_len, prefix_keep_len, suffix_keep_len, top_k, seed
+    "c0": dict(batch=1, kv_heads=2, group=4, head_dim=64, kv_len=700, prefix=16, suffix=33, top_k=96, seed=11),
+    "c1": dict(batch=2, kv_heads=2, group=2, head_dim=128, kv_len=1200, prefix=64, suffix=65, top_k=128, seed=72),
+    "c2": dict(batch=1, kv_heads=1, group=8, head_dim=64, kv_len=300, prefix=0, suffix=1, top_k=500, seed=13),
+    "c3": dict(batch=1, kv_heads=2, group=1, head_dim=128, kv_len=2500, prefix=4, suffix=17, top_k=256, seed=34),
+}
+
+
+def _hash_uniform(n: int, seed: int, salt: int) -> np.ndarray:
+    """n doubles in [0, 1) from a splitmix64-style integer hash of (seed, salt, index)."""
+    with np.errstate(over="ignore"):
+        x = np.arange(n, dtype=np.uint64)
+        x = x + np.uint64((seed * 0x9E3779B97F4A7C15 + salt * 0xD1B54A32D192ED03) & 0xFFFFFFFFFFFFFFFF)
+        x ^= x >> np.uint64(30)
+        x *= np.uint64(0xBF58476D1CE4E5B9)
+        x ^= x >> np.uint64(27)
+        x *= np.uint64(0x94D049BB133111EB)
+        x ^= x >> np.uint64(31)
+    return (x >> np.uint64(40)).astype(np.float64) / float(1 << 24)
+
+
+def _hash_normal(shape, seed: int, salt: int) -> np.ndarray:
+    """Roughly N(0, 1): centred sum of four uniforms (Irwin-Hall), scaled to unit variance."""
+    n = int(np.prod(shape))
+    s = sum(_hash_uniform(n, seed, salt * 4 + j) for j in range(4))
+    return ((s - 2.0) * np.sqrt(3.0)).reshape(shape)
+
+
+def spec_case_inputs(case: dict):
+    """float32 arrays (query [B, H, 1, D], key [B, KV, kv_len, D], value [B, KV, kv_len, D]) in the
+    layout of the attention function of tools/topk_test.py:303-311.
+
+    keys/values: multiples of 1/32 in [-2, 2]; queries: multiples of 1/16 in [-3.9375, 3.9375],
+    each head = 0.5 * (one cached key of its kv head) + noise, so the top-k is not arbitrary."""
+    B, KV, G, D, N, seed = (case[k] for k in ("batch", "kv_heads", "group", "head_dim", "kv_len", "seed"))
+    key = np.clip(np.round(_hash_normal((B, KV, N, D), seed, 1) * 32) / 32, -2, 2)
+    val = np.clip(np.round(_hash_normal((B, KV, N, D), seed, 2) * 32) / 32, -2, 2)
+    pick = (_hash_uniform(B * KV, seed, 99) * N).astype(np.int64).reshape(B, KV)
+    anchor = np.take_along_axis(key, pick[:, :, None, None].repeat(D, axis=3), axis=2)  # [B, KV, 1, D]
+    noise = _hash_normal((B, KV, G, D), seed, 3)
+    q = np.clip(np.round((0.5 * anchor + noise) * 16) / 16, -3.9375, 3.9375)          # [B, KV, G, D]
+    query = q.reshape(B, KV * G, 1, D)
+    return query.astype(np.float32), key.astype(np.float32), val.astype(np.float32)
+
+
+def load_spec_vectors():
+    return np.load(os.path.join(HERE, "golden", "spec_vectors.npz"))
+
+
+def spec_case_split(case: dict, query, key, value):
+    """Maps the [prefix | retrieval | suffix] layout of tools/topk_test.py:355-364 onto the engine's
+    inputs: the store holds the retrieval region, the resident rows are prefix + suffix without its
+    last row, and that last row is the step's new token.  All float32 arrays; returns a dict."""
+    B, KV, G, D, N = (case[k] for k in ("batch", "kv_heads", "group", "head_dim", "kv_len"))
+    p_len = max(0, min(case["prefix"], N))
+    s_len = max(0, min(case["suffix"], N - p_len))
+    assert s_len >= 1, "the newest token is the last row of the suffix"
+    return dict(
+        store_k=np.ascontiguousarray(key[:, :, p_len:N - s_len]), store_v=np.ascontiguousarray(value[:, :, p_len:N - s_len]),
+        res_k=np.ascontiguousarray(np.concatenate([key[:, :, :p_len], key[:, :, N - s_len:N - 1]], axis=2)),
+        res_v=np.ascontiguousarray(np.concatenate([value[:, :, :p_len], value[:, :, N - s_len:N - 1]], axis=2)),
+        k_new=np.ascontiguousarray(key[:, :, N - 1]), v_new=np.ascontiguousarray(value[:, :, N - 1]),
+        q=np.ascontiguousarray(query.reshape(B, KV * G, D)), n_store=N - s_len - p_len, res_rows=p_len + s_len - 1)

@@ -454,6 +454,61 @@ def test_fused_step_edge_cases(oracle_lib):
     eng.close()
 
 
+@pytest.mark.parametrize("name", sorted(util.KVCACHE_CASES))
+def test_kvcache_manager_matches_reference_class(name):
+    """DiffCache against the state the reference's own class (src/diffcache/kvcache/diffcache.py:15-300,
+    run by tests/golden/make_kvcache_vectors.py) reaches on the same inputs: region split, buffer layout
+    [retrieved, right-aligned | prefix | suffix], get_kvcache view, seq_len / seq_len_gpu, suffix
+    bookkeeping — bit for bit; then the fused call must choose the same rows in the same order."""
+    from diffcache_b200 import DiffCache
+
+    c = util.KVCACHE_CASES[name]
+    gold = util.load_kvcache_vectors()
+    L, B, KV, G, D = c["num_layers"], c["batch"], c["kv_heads"], c["group"], c["head_dim"]
+
+    def make():
+        cache = DiffCache(L, B, c["max_length"], KV, KV * G, D, c["budget"], nsw_m=4, nsw_ef_cons=16,
+                          kvbuf_prefix_len=c["prefix"], kvbuf_suffix_len=c["suffix"],
+                          kvbuf_suffix_maxlen=c["suffix_max"], attn_mass_threshold=0.9, k_check_seq=[1048576],
+                          r_sq=[[4.0] * KV for _ in range(L)])
+        for layer in range(L):
+            k, v, _ = util.kvcache_case_inputs(c, layer)
+            cache.prefill_update_kv_cache(torch.from_numpy(k).bfloat16().cuda(), torch.from_numpy(v).bfloat16().cuda(), layer)
+        return cache
+
+    def state(cache):
+        return [cache.kvbuf_prefix_len, cache.kvbuf_suffix_len, cache.retrieval_region_len, cache.seq_len(0),
+                cache.seq_len_gpu(0)]
+
+    cache = make()
+    assert state(cache) == gold[f"{name}_after_prefill"].tolist()
+    for layer in range(L):
+        assert np.allclose(cache.r_sq[layer], gold[f"{name}_l{layer}_r_sq"], rtol=2 ** -7)  # reference sums in bf16
+        q = torch.from_numpy(util.kvcache_case_inputs(c, layer)[2]).bfloat16().cuda()
+        cache.decode_pre_query_operation(q)
+        cache.decode_query_kvcache(layer)
+        cache.decode_post_query_operation(layer)
+        torch.cuda.synchronize()
+        kk, vv = cache.get_kvcache(layer)
+        assert list(kk.shape) == gold[f"{name}_l{layer}_shape"].tolist() == list(vv.shape)
+        rows = gold[f"{name}_l{layer}_k"].shape[1]
+        assert np.array_equal(util.u16(kk[:, :rows]), gold[f"{name}_l{layer}_k"])
+        assert np.array_equal(util.u16(vv[:, :rows]), gold[f"{name}_l{layer}_v"])
+    assert state(cache) == gold[f"{name}_after_step"].tolist()
+
+    fused = make()
+    for layer in range(L):
+        q = torch.from_numpy(util.kvcache_case_inputs(c, layer)[2]).bfloat16().cuda()
+        ef = min(fused.retrieval_region_len, c["budget"])
+        idx = torch.zeros((B, KV, ef), dtype=torch.int32, device="cuda")
+        kn = torch.zeros((B, 1, KV, D), dtype=torch.bfloat16, device="cuda")
+        fused.decode_attention(layer, q, kn, kn.clone(), out_idx=idx)
+        torch.cuda.synchronize()
+        # every dot product of these inputs is exact, so order is identical as well
+        assert np.array_equal(idx.cpu().numpy(), gold[f"{name}_l{layer}_idx"])
+    assert state(fused) == gold[f"{name}_after_step"].tolist()
+
+
 def test_kvcache_manager_flow(oracle_lib):
     """DiffCache (the reference's KV-cache manager API): prefill region split, the three-call
     decode shape and the fused call agree with each other and with the oracle."""

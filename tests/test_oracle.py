@@ -191,3 +191,28 @@ def test_oracle_matches_reference_functional_spec(oracle_lib, name, dtype):
         assert np.all(np.diff(keys_in_ref_order.astype(np.int64)) >= 0)
         assert np.all(np.diff(ref["bits"][p].astype(np.int64)) >= 0)
     np.testing.assert_allclose(ref["out_f32"].reshape(B, 1, KV * G, D), attn, rtol=2e-5, atol=2e-6)
+
+
+@pytest.mark.parametrize("name", sorted(util.KVCACHE_CASES))
+def test_reference_kvcache_layout_fixture(oracle_lib, name):
+    """What the reference's KV-cache manager hands to attention after one decode step
+    (tests/golden/kvcache_vectors.npz, written by running its class) is, per kv head,
+    [top rows of the middle region, best first | first `prefix` tokens | last `suffix` tokens] in the
+    (B, rows, Hkv, D) view of get_kvcache (diffcache.py:186-189), with the rows the oracle selects."""
+    c = util.KVCACHE_CASES[name]
+    gold = util.load_kvcache_vectors()
+    B, KV, G, D, S = c["batch"], c["kv_heads"], c["group"], c["head_dim"], c["seq_len"]
+    p, s = min(c["prefix"], S), min(c["suffix"], S - min(c["prefix"], S))
+    for layer in range(c["num_layers"]):
+        k, v, q = util.kvcache_case_inputs(c, layer)
+        enc = lambda a: oracle_lib.from_f32(np.ascontiguousarray(a, dtype=np.float32), 0)  # noqa: E731
+        mid_k = np.ascontiguousarray(k[:, p:S - s].transpose(0, 2, 1, 3)).reshape(B * KV, S - s - p, D)
+        mid_v = np.ascontiguousarray(v[:, p:S - s].transpose(0, 2, 1, 3)).reshape(B * KV, S - s - p, D)
+        qm = oracle_lib.group_mean(enc(q.reshape(B * KV * G, D)), G, 0)
+        res = oracle_lib.query(enc(mid_k), enc(mid_v), qm, c["budget"], 0)
+        ef = res["ef"]
+        assert ef == min(c["budget"], S - s - p)
+        assert np.array_equal(res["idx"].reshape(B, KV, ef), gold[f"{name}_l{layer}_idx"])
+        for src, got, rows in ((k, gold[f"{name}_l{layer}_k"], res["keys"]), (v, gold[f"{name}_l{layer}_v"], res["vals"])):
+            want = np.concatenate([rows.reshape(B, KV, ef, D).transpose(0, 2, 1, 3), enc(src[:, :p]), enc(src[:, S - s:])], axis=1)
+            assert np.array_equal(got, want)

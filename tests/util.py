@@ -161,3 +161,33 @@ def spec_case_split(case: dict, query, key, value):
         res_v=np.ascontiguousarray(np.concatenate([value[:, :, :p_len], value[:, :, N - s_len:N - 1]], axis=2)),
         k_new=np.ascontiguousarray(key[:, :, N - 1]), v_new=np.ascontiguousarray(value[:, :, N - 1]),
         q=np.ascontiguousarray(query.reshape(B, KV * G, D)), n_store=N - s_len - p_len, res_rows=p_len + s_len - 1)
+
+
+# ---- inputs of the KV-cache-manager fixtures (tests/golden/kvcache_vectors.npz) ----
+
+KVCACHE_CASES = {
+    # long prompt: retrieval region (180) > budget (48); short prompt: retrieval region (20) < budget
+    "long": dict(num_layers=2, batch=1, kv_heads=2, group=4, head_dim=64, seq_len=200, budget=48, prefix=8, suffix=12,
+                 suffix_max=16, max_length=256, seed=21),
+    "short": dict(num_layers=2, batch=2, kv_heads=2, group=4, head_dim=64, seq_len=40, budget=48, prefix=8, suffix=12,
+                  suffix_max=16, max_length=256, seed=22),
+}
+
+
+def kvcache_case_inputs(case: dict, layer: int):
+    """Per layer: key_states, value_states (B, S, Hkv, D) as the model hands them to
+    prefill_update_kv_cache (diffcache.py:149-154) and the decode-step queries (B, 1, Hq*D);
+    float32 arrays whose values are exact in bf16 (same quantisation as spec_case_inputs)."""
+    B, KV, G, D, S = (case[k] for k in ("batch", "kv_heads", "group", "head_dim", "seq_len"))
+    seed = case["seed"] * 100 + layer
+    key = np.clip(np.round(_hash_normal((B, S, KV, D), seed, 1) * 32) / 32, -2, 2)
+    val = np.clip(np.round(_hash_normal((B, S, KV, D), seed, 2) * 32) / 32, -2, 2)
+    pick = (_hash_uniform(B * KV, seed, 99) * S).astype(np.int64).reshape(B, KV)
+    anchor = np.stack([np.stack([key[b, pick[b, h], h] for h in range(KV)]) for b in range(B)])  # (B, KV, D)
+    noise = _hash_normal((B, KV, G, D), seed, 3)
+    q = np.clip(np.round((0.5 * anchor[:, :, None, :] + noise) * 16) / 16, -3.9375, 3.9375)
+    return key.astype(np.float32), val.astype(np.float32), q.reshape(B, 1, KV * G * D).astype(np.float32)
+
+
+def load_kvcache_vectors():
+    return np.load(os.path.join(HERE, "golden", "kvcache_vectors.npz"))

@@ -216,3 +216,15 @@ def test_reference_kvcache_layout_fixture(oracle_lib, name):
         for src, got, rows in ((k, gold[f"{name}_l{layer}_k"], res["keys"]), (v, gold[f"{name}_l{layer}_v"], res["vals"])):
             want = np.concatenate([rows.reshape(B, KV, ef, D).transpose(0, 2, 1, 3), enc(src[:, :p]), enc(src[:, S - s:])], axis=1)
             assert np.array_equal(got, want)
+
+
+def test_k_check_alpha_matches_reference_prototype(oracle_lib):
+    """The exponent the oracle's k-check fits (nsw.rs:198-240) against the reference's Python prototype
+    of the same fit (fit_powerlaw_alpha_from_head, tools/analyze_attn_samples.ipynb; fixture written by
+    tests/golden/make_kcheck_vectors.py)."""
+    gold = util.load_kcheck_vectors()
+    for name, case in util.KCHECK_CASES.items():
+        bits = util.kcheck_case_bits(case)
+        assert bits.shape[0] == gold[name]["n"] and np.all(np.diff(bits.astype(np.int64)) >= 0)
+        _, alpha, _ = oracle_lib.k_check(bits, case["head_dim"], 0.9)
+        assert abs(alpha - gold[name]["alpha"]) <= 1e-4 * max(1.0, abs(gold[name]["alpha"])), (name, alpha)

@@ -191,3 +191,30 @@ def kvcache_case_inputs(case: dict, layer: int):
 
 def load_kvcache_vectors():
     return np.load(os.path.join(HERE, "golden", "kvcache_vectors.npz"))
+
+
+# ---- inputs of the k-check fixtures (tests/golden/kcheck_vectors.json) ----
+
+KCHECK_CASES = {
+    # best-first ranking keys whose logits fall off like -alpha*ln(rank) plus noise
+    "steep": dict(n=64, head_dim=128, alpha=2.5, noise=0.05, top=900.0, seed=31),
+    "shallow": dict(n=256, head_dim=128, alpha=1.05, noise=0.10, top=400.0, seed=32),
+    "short": dict(n=8, head_dim=64, alpha=1.8, noise=0.02, top=120.0, seed=33),
+    "long": dict(n=2048, head_dim=128, alpha=1.4, noise=0.20, top=2000.0, seed=34),
+    "flat": dict(n=100, head_dim=64, alpha=0.0, noise=0.0, top=50.0, seed=35),
+}
+
+
+def kcheck_case_bits(case: dict) -> np.ndarray:
+    """uint32 ranking keys bits(65536 - dot), ascending (best first), of a list whose logits
+    dot/sqrt(D) follow top/sqrt(D) - alpha*ln(rank) + noise."""
+    n, D = case["n"], case["head_dim"]
+    ranks = np.arange(1, n + 1, dtype=np.float64)
+    logit = case["top"] / np.sqrt(D) - case["alpha"] * np.log(ranks) + case["noise"] * _hash_normal((n,), case["seed"], 7)
+    dot = np.sort(logit * np.sqrt(D))[::-1]
+    return (np.float32(65536.0) - dot.astype(np.float32)).astype(np.float32).view(np.uint32)
+
+
+def load_kcheck_vectors():
+    with open(os.path.join(HERE, "golden", "kcheck_vectors.json")) as f:
+        return json.load(f)

@@ -360,7 +360,7 @@ def run_cfg0(cfg, device, steps, warmup):
         st[0].close()
     best = min(per, graph_per) if graph_per else per
     return {"value": 1e3 / best, "ms_per_step": best, "ms_per_step_stream_launch": per, "ms_per_step_cuda_graph": graph_per,
-            "l2_policy": "4 input sets rotated (each 134 MB of K+V, total 537 MB > L2)", "gpu_launches_per_step": 5}
+            "l2_policy": "4 input sets rotated (each 134 MB of K+V, total 537 MB > L2)", "gpu_launches_per_step": 4}
 
 
 def run_cfg2(cfg, world, rank, device, steps, warmup, n_layers=32, hidden=4096):
@@ -403,7 +403,7 @@ def run_cfg2(cfg, world, rank, device, steps, warmup, n_layers=32, hidden=4096):
             "ms_per_step_cuda_graph": per_graph, "layers": n_layers, "hidden": hidden, "output_finite": finite,
             "algorithmic_bytes_per_step": n_layers * cfg.algorithmic_bytes(),
             "parallelism": f"kv-head sharded x{world}; one all-gather of the attention output per layer" if world > 1
-            else "single GPU", "gpu_launches_per_step": 5 * n_layers}
+            else "single GPU", "gpu_launches_per_step": 4 * n_layers}
 
 
 def run_cfg4(cfg, device, steps, warmup, n_sub=16, n_cand=4096):
@@ -587,15 +587,17 @@ def main():
         return
 
     # ---- end to end through the public API with host buffers (e2e) ----
-    q_h = q.cpu().pin_memory()
-    kn_h, vn_h = k_new.cpu().pin_memory(), v_new.cpu().pin_memory()
-    out_h = torch.empty_like(q_h).pin_memory()
-    q_d, kn_d, vn_d = torch.empty_like(q), torch.empty_like(k_new), torch.empty_like(v_new)
+    # q, k_new and v_new of a step leave the host as ONE packed pinned buffer (the layout a fused qkv
+    # projection produces) and land in one device buffer; the three tensors are views into it
+    nq, nk = q.numel(), k_new.numel()
+    in_h = torch.cat([q.reshape(-1), k_new.reshape(-1), v_new.reshape(-1)]).cpu().pin_memory()
+    in_d = torch.empty_like(in_h, device=device)
+    q_d = in_d[:nq].view_as(q)
+    kn_d, vn_d = in_d[nq:nq + nk].view_as(k_new), in_d[nq + nk:].view_as(v_new)
+    out_h = torch.empty_like(q, device="cpu").pin_memory()
 
     def e2e_step():
-        q_d.copy_(q_h, non_blocking=True)
-        kn_d.copy_(kn_h, non_blocking=True)
-        vn_d.copy_(vn_h, non_blocking=True)
+        in_d.copy_(in_h, non_blocking=True)
         eng.decode_attend(q_d, out, cfg.topk, res_k=res_k, res_v=res_v, res_len=res_rows, k_new=kn_d, v_new=vn_d)
         out_h.copy_(out, non_blocking=True)
         torch.cuda.current_stream().synchronize()  # the caller consumes the result of every step
@@ -612,9 +614,7 @@ def main():
         es.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(es):
             with torch.cuda.graph(ge, stream=es):
-                q_d.copy_(q_h, non_blocking=True)
-                kn_d.copy_(kn_h, non_blocking=True)
-                vn_d.copy_(vn_h, non_blocking=True)
+                in_d.copy_(in_h, non_blocking=True)
                 eng.decode_attend(q_d, out, cfg.topk, res_k=res_k, res_v=res_v, res_len=res_rows, k_new=kn_d, v_new=vn_d)
                 out_h.copy_(out, non_blocking=True)
         torch.cuda.current_stream().wait_stream(es)
@@ -676,9 +676,9 @@ def main():
             "phases_ms": {"scan": scan_ms, "select": phases["select_ms"] / max(1, phases["steps"]),
                           "attend": phases["attend_ms"] / max(1, phases["steps"])},
             "e2e": {"value": world * args.steps / (e2e_ms * 1e-3), "unit": UNIT,
-                    "h2d_bytes_per_step": int(q_h.numel() * 2 + kn_h.numel() * 2 + vn_h.numel() * 2),
+                    "h2d_bytes_per_step": int(in_h.numel() * 2),
                     "d2h_bytes_per_step": int(out_h.numel() * 2), "ms_per_step": e2e_ms / args.steps},
-            "gpu_launches": 5 * args.steps,
+            "gpu_launches": 4 * args.steps,
             "timing": {"headline": "cuda_graph_replay" if graph_ms else "stream_launch",
                        "cuda_graph_replay_ms_per_step": graph_ms, "stream_launch_ms_per_step": stream_ms},
             "clocks": clocks,

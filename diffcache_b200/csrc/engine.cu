@@ -20,7 +20,7 @@ int score_scan(const void* keys, int64_t prob_stride, int n_prob, int64_t n, int
                int q_mode, int group, uint32_t* scores, int64_t score_stride, uint32_t* minmax, cudaStream_t stream);
 int topk_select(const uint32_t* bits, const uint32_t* ids, int64_t in_stride, int n_prob, int64_t n, int k,
                 const uint32_t* minmax, uint32_t id_offset, uint32_t* out_bits, uint32_t* out_ids, int64_t out_stride,
-                uint32_t* status, cudaStream_t stream);
+                uint32_t* status, cudaStream_t stream, uint32_t* minmax_reset = nullptr);
 int select_prepare();
 int64_t select_scratch_bytes(int n_prob);
 int sparse_attend(const void* k_store, const void* v_store, int64_t prob_stride, int64_t n_rows, int n_prob,
@@ -195,15 +195,14 @@ int gather_rows(const void* store, int64_t prob_stride, int n_prob, int dim, con
 // out_bits/out_ids (row stride k).  q: device pointer, q_mode as in dc_score_scan.
 int scan_and_select(dc_engine* e, const void* q, int q_mode, int k, uint32_t id_offset, uint32_t* out_bits,
                     uint32_t* out_ids, cudaStream_t s, cudaEvent_t* ev = nullptr) {
-    int rc = init_minmax(e, s);
-    if (rc) return rc;
+    // e->minmax is in its initial state here: set once in dc_create, and put back by every select
     if (ev) DC_CUDA_TRY(cudaEventRecord(ev[0], s));
-    rc = score_scan(e->k, e->prob_stride, e->n_prob, e->ctx_len, e->head_dim, e->dtype, q, q_mode, e->group, e->scores,
+    int rc = score_scan(e->k, e->prob_stride, e->n_prob, e->ctx_len, e->head_dim, e->dtype, q, q_mode, e->group, e->scores,
                     e->score_stride, e->minmax, s);
     if (rc) return rc;
     if (ev) DC_CUDA_TRY(cudaEventRecord(ev[1], s));
     rc = topk_select(e->scores, nullptr, e->score_stride, e->n_prob, e->ctx_len, k, e->minmax, id_offset, out_bits,
-                     out_ids, k, e->status, s);
+                     out_ids, k, e->status, s, e->minmax);
     if (rc) return rc;
     if (ev) DC_CUDA_TRY(cudaEventRecord(ev[2], s));
     return DC_OK;
@@ -304,6 +303,8 @@ int dc_create(int bsz, int q_heads, int kv_heads, int head_dim, int64_t max_ctx_
         return rc;
     }
     int rc = select_prepare();
+    if (rc == DC_OK) rc = init_minmax(e, nullptr);
+    if (rc == DC_OK && cudaDeviceSynchronize() != cudaSuccess) rc = cuda_fail(cudaGetLastError(), "dc_create");
     if (rc) { dc_destroy(e); return rc; }
     *out = e;
     return DC_OK;

@@ -133,9 +133,9 @@ __device__ __forceinline__ void for_each_score(const uint32_t* __restrict__ pb, 
 // dynamic shared memory: out[kpad] u64 | cand[kCandCap] u64 | hist[kBins] u32 | cum[kBins] u32 | raw[raw_cap] u64
 __global__ void __launch_bounds__(kSelThreads, 1)
 topk_select_kernel(const uint32_t* __restrict__ bits, const uint32_t* __restrict__ ids, int64_t in_stride, int64_t n,
-                   int k, const uint32_t* __restrict__ minmax, uint32_t id_offset, uint32_t* __restrict__ out_bits,
-                   uint32_t* __restrict__ out_ids, int64_t out_stride, int kpad, int raw_cap,
-                   uint32_t* __restrict__ status) {
+                   int k, const uint32_t* minmax, uint32_t* minmax_reset, uint32_t id_offset,
+                   uint32_t* __restrict__ out_bits, uint32_t* __restrict__ out_ids, int64_t out_stride, int kpad,
+                   int raw_cap, uint32_t* __restrict__ status) {
     cg::cluster_group cluster = cg::this_cluster();
     const unsigned rank = cluster.block_rank();
     const unsigned csize = cluster.num_blocks();
@@ -483,6 +483,8 @@ topk_select_kernel(const uint32_t* __restrict__ bits, const uint32_t* __restrict
     }
     cluster.sync();  // all remote writes into the leader have landed
     if (rank != 0) return;
+    // every CTA read the key range long ago: hand the pair back in the state the next scan folds into
+    if (minmax_reset != nullptr && tid == 0) { minmax_reset[2 * prob] = 0xFFFFFFFFu; minmax_reset[2 * prob + 1] = 0u; }
 
     // ---- leader: resolve the threshold bin, sort, write ----
     if (!take_all && !single_value) {
@@ -558,9 +560,11 @@ int select_prepare() {
     return DC_OK;
 }
 
+// minmax_reset (may be NULL, may alias minmax): per-problem (min, max) pairs that the kernel sets back
+// to (0xFFFFFFFF, 0) once it has read them, ready for the next scan's atomic min / max.
 int topk_select(const uint32_t* bits, const uint32_t* ids, int64_t in_stride, int n_prob, int64_t n, int k,
                 const uint32_t* minmax, uint32_t id_offset, uint32_t* out_bits, uint32_t* out_ids, int64_t out_stride,
-                uint32_t* status, cudaStream_t stream) {
+                uint32_t* status, cudaStream_t stream, uint32_t* minmax_reset) {
     DC_REQUIRE(bits != nullptr, "topk_select: null scores");
     DC_REQUIRE(k >= 0 && k <= DC_MAX_TOPK, "topk_select: k=%d outside [0, %d]", k, DC_MAX_TOPK);
     DC_REQUIRE(n >= 0 && n < (1ll << 32), "topk_select: n=%lld outside [0, 2^32)", static_cast<long long>(n));
@@ -594,8 +598,8 @@ int topk_select(const uint32_t* bits, const uint32_t* ids, int64_t in_stride, in
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    DC_CUDA_TRY(cudaLaunchKernelEx(&cfg, topk_select_kernel, bits, ids, in_stride, n, k, minmax, id_offset, out_bits,
-                                   out_ids, out_stride, kpad, raw_cap, status));
+    DC_CUDA_TRY(cudaLaunchKernelEx(&cfg, topk_select_kernel, bits, ids, in_stride, n, k, minmax, minmax_reset, id_offset,
+                                   out_bits, out_ids, out_stride, kpad, raw_cap, status));
     return DC_OK;
 }
 

@@ -17,7 +17,8 @@ namespace dc {
 
 // ---- kernels defined in the other translation units ----
 int score_scan(const void* keys, int64_t prob_stride, int n_prob, int64_t n, int head_dim, int dtype, const void* q,
-               int q_mode, int group, uint32_t* scores, int64_t score_stride, uint32_t* minmax, cudaStream_t stream);
+               int q_mode, int group, uint32_t* scores, int64_t score_stride, uint32_t* minmax, cudaStream_t stream,
+               uint32_t* status = nullptr);
 int topk_select(const uint32_t* bits, const uint32_t* ids, int64_t in_stride, int n_prob, int64_t n, int k,
                 const uint32_t* minmax, uint32_t id_offset, uint32_t* out_bits, uint32_t* out_ids, int64_t out_stride,
                 uint32_t* status, cudaStream_t stream, uint32_t* minmax_reset = nullptr);
@@ -198,7 +199,7 @@ int scan_and_select(dc_engine* e, const void* q, int q_mode, int k, uint32_t id_
     // e->minmax is in its initial state here: set once in dc_create, and put back by every select
     if (ev) DC_CUDA_TRY(cudaEventRecord(ev[0], s));
     int rc = score_scan(e->k, e->prob_stride, e->n_prob, e->ctx_len, e->head_dim, e->dtype, q, q_mode, e->group, e->scores,
-                    e->score_stride, e->minmax, s);
+                    e->score_stride, e->minmax, s, e->status);
     if (rc) return rc;
     if (ev) DC_CUDA_TRY(cudaEventRecord(ev[1], s));
     rc = topk_select(e->scores, nullptr, e->score_stride, e->n_prob, e->ctx_len, k, e->minmax, id_offset, out_bits,

@@ -2,11 +2,20 @@
 //
 // Replaces the loop body of Index::search_bruteforce (diffcache_cpu/src/nsw.rs:601-607)
 // with Index::distance QKDist (nsw.rs:129-139): one 256-byte row read + 128 MACs per key,
-// done here as a pure HBM stream.  The store is read exactly once with 16-byte loads that
-// are contiguous across the warp (each load instruction covers 512 contiguous bytes), the
-// dot products are accumulated in fp32 on the CUDA cores (this is a GEMV: one query vector
-// per key stream, so there is no dense contraction to hand to the tensor cores), and the
-// only thing written back is one 4-byte ranking key per row (1.6 % of the bytes read).
+// done here as a pure HBM stream.  The store is read exactly once, the dot products are
+// accumulated in fp32 on the CUDA cores (this is a GEMV: one query vector per key stream, so
+// there is no dense contraction to hand to the tensor cores), and the only thing written back
+// is one 4-byte ranking key per row (1.6 % of the bytes read).
+//
+// Three kernels compute the same thing (selected by the environment variable DC_SCAN_VARIANT):
+//   "wide"   (default) 32-byte global loads, each warp-wide load covers 1 KB of consecutive rows;
+//   "narrow" 16-byte global loads (512 B per warp-wide load);
+//   "tma"    rows brought in by the TMA engine, one 32 KB cp.async.bulk per stage of a shared-memory
+//            ring completing on mbarriers, one producer warp and eight consumer warps per persistent
+//            CTA; bit-identical to "narrow".  Measured slower than the register loads (0.626 ms against
+//            0.599 ms for 4.28 GB of keys), which is why it is not the default.
+#include <cstdlib>
+#include <cstring>
 #include <cstdlib>
 
 #include "common.cuh"
@@ -177,6 +186,155 @@ score_scan_wide_kernel(const uint16_t* __restrict__ keys, int64_t prob_stride, i
     }
 }
 
+// ---- the same scan fed by the TMA engine ----
+constexpr int kTmaConsWarps = 8;
+constexpr int kTmaThreads = (kTmaConsWarps + 1) * 32;
+constexpr int kTmaStages = 4;
+constexpr int kTmaStageBytes = 32 * 1024;
+
+__device__ __forceinline__ void mbar_arrive(unsigned long long* bar) {
+    asm volatile("{\n .reg .b64 st;\n mbarrier.arrive.shared::cta.b64 st, [%0];\n}\n" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// Persistent CTAs; work unit u = one stage (32 KB of consecutive rows of one problem), unit u goes to
+// CTA u % gridDim.x so that the CTAs of the grid read one contiguous window of the store at a time.
+// Warp kTmaConsWarps is the producer: one lane waits for a free stage and issues ONE bulk copy for it.
+// The consumer warps each own 1/8 of the stage's rows (exactly one warp tile), pull them into registers,
+// release the stage, and then do the arithmetic of score_scan_kernel.  Every mbarrier wait is bounded;
+// a wait that runs out stores 201 (producer) or 202 (consumer) in *status and the thread leaves.
+template <int DT, int LPR>
+__global__ void __launch_bounds__(kTmaThreads, 1)
+score_scan_tma_kernel(const uint16_t* __restrict__ keys, int64_t prob_stride, int64_t n, int n_prob,
+                      const uint16_t* __restrict__ q, int q_mode, int group, uint32_t* __restrict__ scores,
+                      int64_t score_stride, uint32_t* __restrict__ minmax, uint32_t* __restrict__ status,
+                      int q_table) {
+    constexpr int D = LPR * 8;
+    constexpr int R = 32 / LPR;
+    constexpr int TR = kLoadsPerTile * R;
+    constexpr int STAGE_ROWS = kTmaStageBytes / (D * 2);
+    static_assert(STAGE_ROWS == kTmaConsWarps * TR, "a stage is one warp tile per consumer warp");
+    extern __shared__ __align__(128) unsigned char tma_ring[];
+    __shared__ unsigned long long full[kTmaStages], empty[kTmaStages];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t units_per_prob = (n + STAGE_ROWS - 1) / STAGE_ROWS;
+    const int64_t total = units_per_prob * n_prob;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kTmaStages; s++) { mbar_init(&full[s], 1); mbar_init(&empty[s], kTmaConsWarps); }
+        mbar_init_fence();
+    }
+    // A CTA meets every problem (a few stages of each), so the retrieval queries of all problems are formed
+    // once into shared memory behind the ring (q_table != 0: they fit) instead of at every change of problem.
+    uint16_t* s_q = reinterpret_cast<uint16_t*>(tma_ring + static_cast<size_t>(kTmaStages) * kTmaStageBytes);
+    if (q_table) {
+        for (int i = threadIdx.x; i < n_prob * LPR; i += kTmaThreads) {
+            float f[8];
+            load_query8<DT>(q, i / LPR, D, q_mode, group, (i % LPR) * 8, f);
+            uint4 w;
+            w.x = float_to_elem<DT>(f[0]) | (static_cast<uint32_t>(float_to_elem<DT>(f[1])) << 16);
+            w.y = float_to_elem<DT>(f[2]) | (static_cast<uint32_t>(float_to_elem<DT>(f[3])) << 16);
+            w.z = float_to_elem<DT>(f[4]) | (static_cast<uint32_t>(float_to_elem<DT>(f[5])) << 16);
+            w.w = float_to_elem<DT>(f[6]) | (static_cast<uint32_t>(float_to_elem<DT>(f[7])) << 16);
+            *reinterpret_cast<uint4*>(s_q + static_cast<size_t>(i) * 8) = w;
+        }
+    }
+    // ... and its (min, max) pairs are gathered in shared memory and folded into global memory once, at the
+    // end: all CTAs change problem at about the same time, and 8 warps x all CTAs firing atomics at the same
+    // two words at once was measured to cost more than 100 us per scan.
+    uint32_t* s_mm = reinterpret_cast<uint32_t*>(s_q + static_cast<size_t>(n_prob) * LPR * 8);
+    if (q_table)
+        for (int i = threadIdx.x; i < n_prob; i += kTmaThreads) { s_mm[2 * i] = 0xFFFFFFFFu; s_mm[2 * i + 1] = 0u; }
+    __syncthreads();
+    if (warp == kTmaConsWarps) {
+        if (lane == 0) {
+            int64_t it = 0;
+            for (int64_t u = blockIdx.x; u < total; u += gridDim.x, it++) {
+                const int s = static_cast<int>(it % kTmaStages);
+                if (it >= kTmaStages && !mbar_wait_bounded(&empty[s], static_cast<unsigned>((it / kTmaStages - 1) & 1))) {
+                    if (status) atomicMax(status, 201u);
+                    break;
+                }
+                const int64_t p = u / units_per_prob, r0 = (u % units_per_prob) * STAGE_ROWS;
+                const unsigned bytes = static_cast<unsigned>(min(static_cast<int64_t>(STAGE_ROWS), n - r0)) * D * 2;
+                mbar_arrive_expect_tx(&full[s], bytes);
+                bulk_copy_g2s(tma_ring + static_cast<size_t>(s) * kTmaStageBytes, keys + p * prob_stride + r0 * D, bytes,
+                              &full[s]);
+            }
+        }
+        return;
+    }
+    const int col = lane % LPR, sub = lane / LPR;
+    const int my_i = treduce_base<kLoadsPerTile, LPR>(lane);
+    const bool writer = (col & ((1 << treduce_plain_bits<kLoadsPerTile, LPR>()) - 1)) == 0;
+    uint32_t lo = 0xFFFFFFFFu, hi = 0u;
+    int64_t cur_p = -1;
+    auto flush_minmax = [&]() {  // warp-uniform
+        lo = __reduce_min_sync(0xFFFFFFFFu, lo);
+        hi = __reduce_max_sync(0xFFFFFFFFu, hi);
+        if (minmax != nullptr && lane == 0 && lo <= hi) {
+            uint32_t* mm = q_table ? s_mm : minmax;
+            atomicMin(&mm[2 * cur_p], lo);
+            atomicMax(&mm[2 * cur_p + 1], hi);
+        }
+        lo = 0xFFFFFFFFu; hi = 0u;
+    };
+    float qv[8];
+    int64_t it = 0;
+    for (int64_t u = blockIdx.x; u < total; u += gridDim.x, it++) {
+        const int s = static_cast<int>(it % kTmaStages);
+        const int64_t p = u / units_per_prob, r0 = (u % units_per_prob) * STAGE_ROWS;
+        if (p != cur_p) {
+            if (cur_p >= 0) flush_minmax();
+            cur_p = p;
+            if (q_table) unpack8<DT>(*reinterpret_cast<const uint4*>(s_q + (p * LPR + col) * 8), qv);
+            else load_query8<DT>(q, p, D, q_mode, group, col * 8, qv);
+        }
+        // warp-uniform outcome: either every lane saw the stage arrive or the whole warp gives up
+        if (!__all_sync(0xFFFFFFFFu, mbar_wait_bounded(&full[s], static_cast<unsigned>((it / kTmaStages) & 1)))) {
+            if (status && lane == 0) atomicMax(status, 202u);
+            break;
+        }
+        const int rows = static_cast<int>(min(static_cast<int64_t>(STAGE_ROWS), n - r0));
+        const unsigned char* st = tma_ring + static_cast<size_t>(s) * kTmaStageBytes;
+        uint4 w[kLoadsPerTile];
+#pragma unroll
+        for (int i = 0; i < kLoadsPerTile; i++) {
+            const int r = warp * TR + i * R + sub;
+            w[i] = *reinterpret_cast<const uint4*>(st + (static_cast<size_t>(r) * D + col * 8) * 2);
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty[s]);  // the rows are in registers: the producer may refill the stage
+        float part[kLoadsPerTile];
+#pragma unroll
+        for (int i = 0; i < kLoadsPerTile; i++) {
+            float f[8];
+            unpack8<DT>(w[i], f);
+            float a = f[0] * qv[0];
+#pragma unroll
+            for (int j = 1; j < 8; j++) a = fmaf(f[j], qv[j], a);
+            part[i] = a;
+        }
+        treduce<kLoadsPerTile, LPR>(part, lane);
+        const int r = warp * TR + my_i * R + sub;
+        if (writer && r < rows) {   // rows past the end of the problem hold stale bytes of an earlier stage
+            const uint32_t b = dist_bits(part[0]);
+            scores[p * score_stride + r0 + r] = b;
+            lo = min(lo, b);
+            hi = max(hi, b);
+        }
+    }
+    if (cur_p >= 0) flush_minmax();
+    if (q_table && minmax != nullptr) {
+        // the consumer warps only (the producer warp has left): named barrier 1, kTmaConsWarps * 32 threads
+        asm volatile("bar.sync 1, %0;\n" ::"n"(kTmaConsWarps * 32) : "memory");
+        for (int i = threadIdx.x; i < n_prob; i += kTmaConsWarps * 32) {
+            if (s_mm[2 * i] <= s_mm[2 * i + 1]) {
+                atomicMin(&minmax[2 * i], s_mm[2 * i]);
+                atomicMax(&minmax[2 * i + 1], s_mm[2 * i + 1]);
+            }
+        }
+    }
+}
+
 int env_int(const char* name, int dflt) {
     const char* s = std::getenv(name);
     if (s == nullptr || *s == 0) return dflt;
@@ -185,14 +343,35 @@ int env_int(const char* name, int dflt) {
 
 template <int DT, int LPR>
 int launch_scan(const void* keys, int64_t prob_stride, int n_prob, int64_t n, const void* q, int q_mode, int group,
-                uint32_t* scores, int64_t score_stride, uint32_t* minmax, cudaStream_t stream) {
+                uint32_t* scores, int64_t score_stride, uint32_t* minmax, uint32_t* status, cudaStream_t stream) {
     constexpr int TR = kLoadsPerTile * (32 / LPR);
     static int rows_cfg = env_int("DC_SCAN_ROWS_PER_CTA", 1024);
     int rows_per_cta = ((rows_cfg + kScanWarps * TR - 1) / (kScanWarps * TR)) * (kScanWarps * TR);
     int64_t chunks = (n + rows_per_cta - 1) / rows_per_cta;
     dim3 grid(static_cast<unsigned>(chunks), static_cast<unsigned>(n_prob));
-    static int wide = env_int("DC_SCAN_WIDE", 1);
-    if (wide && LPR >= 8 && prob_stride % 16 == 0 && (reinterpret_cast<uintptr_t>(keys) & 31) == 0) {
+    const char* variant = std::getenv("DC_SCAN_VARIANT");  // read per call: "wide" (default), "narrow", "tma"
+    const bool want_tma = variant != nullptr && std::strcmp(variant, "tma") == 0;
+    const bool want_narrow = variant != nullptr && std::strcmp(variant, "narrow") == 0;
+    if (want_tma) {
+        static bool ready[64] = {};
+        int dev = 0;
+        DC_CUDA_TRY(cudaGetDevice(&dev));
+        constexpr int kRing = kTmaStages * kTmaStageBytes;
+        constexpr int kQTableMax = 64 * 1024;   // ring + table stay below the 227 KB a CTA may use
+        if (dev < 0 || dev >= 64 || !ready[dev]) {
+            DC_CUDA_TRY(cudaFuncSetAttribute(score_scan_tma_kernel<DT, LPR>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             kRing + kQTableMax));
+            if (dev >= 0 && dev < 64) ready[dev] = true;
+        }
+        const size_t table_bytes = static_cast<size_t>(n_prob) * (LPR * 16 + 8);   // queries + (min, max) pairs
+        const int q_table = table_bytes <= static_cast<size_t>(kQTableMax) ? 1 : 0;
+        score_scan_tma_kernel<DT, LPR><<<sm_count(), kTmaThreads, kRing + (q_table ? table_bytes : 0), stream>>>(
+            static_cast<const uint16_t*>(keys), prob_stride, n, n_prob, static_cast<const uint16_t*>(q), q_mode, group,
+            scores, score_stride, minmax, status, q_table);
+        DC_CUDA_TRY(cudaGetLastError());
+        return DC_OK;
+    }
+    if (!want_narrow && LPR >= 8 && prob_stride % 16 == 0 && (reinterpret_cast<uintptr_t>(keys) & 31) == 0) {
         // rows_per_cta is a multiple of 8 warps x 8 loads x (32 / (LPR/2)) rows as well (LPR >= 8)
         score_scan_wide_kernel<DT, LPR / 2><<<grid, kScanThreads, 0, stream>>>(
             static_cast<const uint16_t*>(keys), prob_stride, n, static_cast<const uint16_t*>(q), q_mode, group, scores,
@@ -210,7 +389,8 @@ int launch_scan(const void* keys, int64_t prob_stride, int n_prob, int64_t n, co
 }  // namespace
 
 int score_scan(const void* keys, int64_t prob_stride, int n_prob, int64_t n, int head_dim, int dtype, const void* q,
-               int q_mode, int group, uint32_t* scores, int64_t score_stride, uint32_t* minmax, cudaStream_t stream) {
+               int q_mode, int group, uint32_t* scores, int64_t score_stride, uint32_t* minmax, cudaStream_t stream,
+               uint32_t* status) {
     DC_REQUIRE(keys && q && scores, "score_scan: null pointer");
     DC_REQUIRE(dtype == DC_BF16 || dtype == DC_FP16, "score_scan: dtype %d not supported", dtype);
     DC_REQUIRE(head_dim == 64 || head_dim == 128 || head_dim == 256, "score_scan: head_dim %d not in {64,128,256}",
@@ -223,7 +403,8 @@ int score_scan(const void* keys, int64_t prob_stride, int n_prob, int64_t n, int
                "score_scan: keys/q must be 16-byte aligned and prob_stride a multiple of 8 elements");
     if (n_prob == 0 || n == 0) return DC_OK;
 #define DC_SCAN_CASE(DT, LPR) \
-    return launch_scan<DT, LPR>(keys, prob_stride, n_prob, n, q, q_mode, group, scores, score_stride, minmax, stream)
+    return launch_scan<DT, LPR>(keys, prob_stride, n_prob, n, q, q_mode, group, scores, score_stride, minmax, status, \
+                                stream)
     if (dtype == DC_BF16) {
         if (head_dim == 64) DC_SCAN_CASE(DC_BF16, 8);
         if (head_dim == 128) DC_SCAN_CASE(DC_BF16, 16);

@@ -63,6 +63,38 @@ def test_scan_matches_oracle(lib, oracle_lib, dtype, D):
             assert mm[p, 0] == got[p].min() and mm[p, 1] == got[p].max()
 
 
+@pytest.mark.parametrize("dtype", ["bf16", "fp16"])
+@pytest.mark.parametrize("D", [64, 128, 256])
+def test_scan_variants_agree(lib, monkeypatch, dtype, D):
+    """The three scan kernels (DC_SCAN_VARIANT = wide | narrow | tma): the TMA-fed kernel sums in the
+    order of the 16-byte-load kernel and must reproduce it bit for bit, min/max included; the 32-byte-load
+    kernel sums in another order and may differ by one ulp of dist.  Ragged sizes around the 32 KB stage."""
+    dt = util.dtype_code(dtype)
+    stage_rows = 32768 // (2 * D)
+    for n in (1, stage_rows - 1, stage_rows, stage_rows + 1, 5 * stage_rows + 7, 40000):
+        k, _, q = util.small_problem(1, 3, 4, n, D, seed=500 + n, dtype=dtype)
+        kd, qd = k.cuda().reshape(3, n, D), q.cuda().contiguous()
+        got = {}
+        for variant in ("narrow", "tma", "wide"):
+            monkeypatch.setenv("DC_SCAN_VARIANT", variant)
+            got[variant] = _scan(lib, kd, qd, n, D, dt, 1, 4)
+        monkeypatch.delenv("DC_SCAN_VARIANT")
+        assert np.array_equal(got["tma"][0], got["narrow"][0]) and np.array_equal(got["tma"][1], got["narrow"][1])
+        a = got["wide"][0].view(np.float32).astype(np.float64)
+        b = got["narrow"][0].view(np.float32).astype(np.float64)
+        assert np.all(np.abs(a - b) <= util.ulp_of_dist(got["narrow"][0]))
+    # more problems than the TMA kernel's shared-memory query table holds (it then loads q per problem)
+    P = 65536 // (2 * D) + 44
+    k, _, q = util.small_problem(P // 4, 4, 2, 70, D, seed=77, dtype=dtype)
+    kd, qd = k.cuda().reshape(P, 70, D), q.cuda().contiguous()
+    got = {}
+    for variant in ("narrow", "tma"):
+        monkeypatch.setenv("DC_SCAN_VARIANT", variant)
+        got[variant] = _scan(lib, kd, qd, 70, D, dt, 1, 2)
+    monkeypatch.delenv("DC_SCAN_VARIANT")
+    assert np.array_equal(got["tma"][0], got["narrow"][0]) and np.array_equal(got["tma"][1], got["narrow"][1])
+
+
 def test_scan_group_mean_matches_torch_cuda_mean(lib):
     """q_mode 1 (mean formed in the kernel) must equal scanning with torch's CUDA mean, the
     operation the reference runs at src/diffcache/kvcache/diffcache.py:193 — bit for bit."""

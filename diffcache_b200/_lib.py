@@ -34,7 +34,8 @@ SIGNATURES = {
     "dc_get_phase_times": (_i32, [_vp, ctypes.POINTER(_f32), ctypes.POINTER(_f32), ctypes.POINTER(_f32),
                                   ctypes.POINTER(_i32)]),
     "dc_local_topk": (_i32, [_vp, _vp, _i32, _vp, _vp, _u64]),
-    "dc_attend_owned": (_i32, [_vp, _vp, _vp, _i32, _vp, _vp, _vp, _vp, _i64, _i64, _i32, _f32, _vp, _vp, _u64]),
+    "dc_attend_owned": (_i32, [_vp, _vp, _vp, _i32, _vp, _vp, _vp, _vp, _i64, _i64, _i32, _f32, _vp, _vp, _vp, _u64]),
+    "dc_merge_sorted_count": (_i32, [_vp, _i32, _i32, _i32, _i32, _vp, _u64]),
     "dc_score_scan": (_i32, [_vp, _i64, _i32, _i64, _i32, _i32, _vp, _i32, _i32, _vp, _i64, _vp, _u64]),
     "dc_select_scratch_bytes": (_i64, [_i32]),
     "dc_topk_select": (_i32, [_vp, _vp, _i64, _i32, _i64, _i32, _vp, _vp, _vp, _i64, _vp, _u64]),

@@ -24,6 +24,8 @@ int topk_select(const uint32_t* bits, const uint32_t* ids, int64_t in_stride, in
                 uint32_t* status, cudaStream_t stream, uint32_t* minmax_reset = nullptr);
 int select_prepare();
 int64_t select_scratch_bytes(int n_prob);
+int merge_sorted_count(const uint32_t* bits_all, int world, int n_prob, int k, int my_rank, int32_t* out_count,
+                       cudaStream_t stream);
 int sparse_attend(const void* k_store, const void* v_store, int64_t prob_stride, int64_t n_rows, int n_prob,
                   int kv_heads, int group, int head_dim, int dtype, const void* q, const uint32_t* sel,
                   int64_t sel_stride, int n_sel, int64_t sel_base, const void* k_new, const void* v_new, void* res_k,
@@ -588,13 +590,14 @@ int dc_local_topk(dc_engine* e, const void* q, int topk, uint32_t* out_bits, uin
 
 int dc_attend_owned(dc_engine* e, const void* q, const uint32_t* sel_gidx, int n_sel, const void* k_new,
                     const void* v_new, void* res_k, void* res_v, int64_t res_stride_b, int64_t res_stride_h,
-                    int res_len, float scale, float* out_acc, float* out_ml, uint64_t stream) {
+                    int res_len, float scale, float* out_acc, float* out_ml, const int32_t* sel_count,
+                    uint64_t stream) {
     DC_ENGINE_ENTER(e);
     DC_REQUIRE(q && out_acc && out_ml, "dc_attend_owned: null pointer");
     return sparse_attend(e->k, e->v, e->prob_stride, e->ctx_len, e->n_prob, e->kv_heads, e->group, e->head_dim,
                          e->dtype, q, sel_gidx, n_sel, n_sel, e->row_offset, k_new, v_new, res_k, res_v, res_stride_b,
                          res_stride_h, res_len, scale, nullptr, nullptr, out_acc, out_ml, e->att_scratch,
-                         as_stream(stream));
+                         as_stream(stream), sel_count);
 }
 
 // ---- stateless kernels ----
@@ -606,6 +609,11 @@ int dc_score_scan(const void* keys, int64_t prob_stride, int n_prob, int64_t n, 
 }
 
 int64_t dc_select_scratch_bytes(int n_prob) { return select_scratch_bytes(n_prob); }
+
+int dc_merge_sorted_count(const uint32_t* bits_all, int world, int n_prob, int k, int my_rank, int32_t* out_count,
+                          uint64_t stream) {
+    return merge_sorted_count(bits_all, world, n_prob, k, my_rank, out_count, as_stream(stream));
+}
 
 int dc_topk_select(const uint32_t* bits, const uint32_t* ids, int64_t in_stride, int n_prob, int64_t n, int k,
                    const uint32_t* minmax, uint32_t* out_bits, uint32_t* out_ids, int64_t out_stride, void* scratch,

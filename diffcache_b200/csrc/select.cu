@@ -543,7 +543,86 @@ topk_select_kernel(const uint32_t* __restrict__ bits, const uint32_t* __restrict
 
 int pow2_floor(int x) { int p = 1; while (p * 2 <= x) p *= 2; return p; }
 
+// ---- merge of per-rank sorted candidate lists without moving ids ----
+// Sequence-sharded search: every rank holds, per problem, its own k best ranking keys in ascending order, and
+// has received the lists of all ranks ((world, n_prob, k), 0xFFFFFFFF pads).  Because each list is sorted, the
+// global k best that rank r owns are a PREFIX of its list; this kernel returns the length of that prefix for
+// `my_rank`.  The global rank of my i-th key b is i + sum over lower ranks of #(keys <= b) + sum over higher
+// ranks of #(keys < b): rows of a lower rank have smaller global ids, so on equal dist bits they come first —
+// the reference's tie rule (nsw.rs:74-91,612) restated for contiguous row shards.  Lists live in shared
+// memory (world * k * 4 bytes); one CTA per problem.
+constexpr int kMergeThreads = 1024;
+
+__global__ void __launch_bounds__(kMergeThreads)
+merge_sorted_count_kernel(const uint32_t* __restrict__ bits_all, int world, int n_prob, int k, int my_rank,
+                          int32_t* __restrict__ out_count) {
+    extern __shared__ __align__(16) uint32_t s_lists[];
+    __shared__ int s_sum[kMergeThreads / 32];
+    const int p = blockIdx.x, tid = threadIdx.x;
+    for (int r = 0; r < world; r++) {
+        const uint32_t* src = bits_all + (static_cast<int64_t>(r) * n_prob + p) * k;
+        uint32_t* dst = s_lists + static_cast<size_t>(r) * k;
+        if ((k & 3) == 0 && (reinterpret_cast<uintptr_t>(src) & 15) == 0) {
+            for (int i = tid; i < k / 4; i += kMergeThreads)
+                reinterpret_cast<uint4*>(dst)[i] = reinterpret_cast<const uint4*>(src)[i];
+        } else {
+            for (int i = tid; i < k; i += kMergeThreads) dst[i] = src[i];
+        }
+    }
+    __syncthreads();
+    const uint32_t* mine = s_lists + static_cast<size_t>(my_rank) * k;
+    int winners = 0;
+    for (int i = tid; i < k; i += kMergeThreads) {
+        const uint32_t b = mine[i];
+        if (b == 0xFFFFFFFFu) continue;  // pad: this rank holds fewer than k rows
+        uint32_t rank = static_cast<uint32_t>(i);
+        for (int r = 0; r < world && rank < static_cast<uint32_t>(k); r++) {
+            if (r == my_rank) continue;
+            const uint32_t* list = s_lists + static_cast<size_t>(r) * k;
+            // lower ranks: keys <= b; higher ranks: keys < b, i.e. keys <= b - 1 (none when b == 0)
+            const uint32_t bound = r < my_rank ? b : b - 1u;
+            int lo = 0, hi = (r > my_rank && b == 0u) ? 0 : k;
+            while (lo < hi) {
+                const int mid = (lo + hi) >> 1;
+                if (list[mid] <= bound) lo = mid + 1; else hi = mid;
+            }
+            rank += static_cast<uint32_t>(lo);
+        }
+        if (rank < static_cast<uint32_t>(k)) winners++;
+    }
+    winners = __reduce_add_sync(0xFFFFFFFFu, winners);
+    if ((tid & 31) == 0) s_sum[tid >> 5] = winners;
+    __syncthreads();
+    if (tid == 0) {
+        int total = 0;
+        for (int w = 0; w < kMergeThreads / 32; w++) total += s_sum[w];
+        out_count[p] = total;
+    }
+}
+
 }  // namespace
+
+int merge_sorted_count(const uint32_t* bits_all, int world, int n_prob, int k, int my_rank, int32_t* out_count,
+                       cudaStream_t stream) {
+    DC_REQUIRE(bits_all && out_count, "merge_sorted_count: null pointer");
+    DC_REQUIRE(world >= 1 && my_rank >= 0 && my_rank < world, "merge_sorted_count: rank %d of %d", my_rank, world);
+    DC_REQUIRE(k >= 1 && k <= DC_MAX_TOPK, "merge_sorted_count: k=%d outside [1, %d]", k, DC_MAX_TOPK);
+    DC_REQUIRE(n_prob >= 0 && n_prob <= 65535, "merge_sorted_count: n_prob=%d", n_prob);
+    const size_t smem = static_cast<size_t>(world) * k * sizeof(uint32_t);
+    DC_REQUIRE(smem <= 200 * 1024, "merge_sorted_count: world*k=%lld keys do not fit the 200 KB of shared memory",
+               static_cast<long long>(world) * k);
+    if (n_prob == 0) return DC_OK;
+    static bool done[64] = {};
+    int dev = 0;
+    DC_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64 || !done[dev]) {
+        DC_CUDA_TRY(cudaFuncSetAttribute(merge_sorted_count_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        if (dev >= 0 && dev < 64) done[dev] = true;
+    }
+    merge_sorted_count_kernel<<<n_prob, kMergeThreads, smem, stream>>>(bits_all, world, n_prob, k, my_rank, out_count);
+    DC_CUDA_TRY(cudaGetLastError());
+    return DC_OK;
+}
 
 int64_t select_scratch_bytes(int n_prob) { (void)n_prob; return 256; }
 

@@ -297,11 +297,11 @@ class DiffCacheGPU:
                                            _current_stream(stream)))
 
     def attend_owned(self, q, sel_gidx, n_sel: int, out_acc, out_ml, res_k=None, res_v=None, res_len: int = 0,
-                     k_new=None, v_new=None, scale: float = 0.0, stream=None) -> None:
+                     k_new=None, v_new=None, scale: float = 0.0, stream=None, sel_count=None) -> None:
         sb = sh = 0
         if res_k is not None:
             st = tuple(res_k.stride())
             sb, sh = st[0], st[1]
         _lib.check(self._lib.dc_attend_owned(self._h, _ptr(q), _ptr(sel_gidx), int(n_sel), _ptr(k_new), _ptr(v_new),
                                              _ptr(res_k), _ptr(res_v), sb, sh, int(res_len), float(scale),
-                                             _ptr(out_acc), _ptr(out_ml), _current_stream(stream)))
+                                             _ptr(out_acc), _ptr(out_ml), _ptr(sel_count), _current_stream(stream)))

@@ -5,10 +5,10 @@ offloading to host memory.  On an 8-GPU box the same step shards instead:
 
 * :class:`SequenceShardedStep` — one very long sequence (1M tokens): the retrieval region is cut
   into contiguous row ranges, one per rank.  Per step every rank scans its rows and selects a
-  local top-k; the ``(dist bits, global row id)`` candidates are all-gathered (k*8 bytes per
-  kv head and rank) and every rank runs the identical merge select, so all ranks agree on the
-  global top-k (same total order, ties to the smaller global id); each rank then attends over the
-  selected rows it owns (rank 0 adds the sink rows, the last rank the local window and the new
+  local top-k, sorted; the ranking keys are all-gathered (k*4 bytes per kv head and rank) and
+  every rank counts how long a prefix of its own list belongs to the global top-k (same total
+  order, ties to the smaller global id, which for contiguous shards means to the lower rank); each
+  rank then attends over that prefix (rank 0 adds the sink rows, the last rank the local window and the new
   token) and the un-normalised partial results ``(acc, max, sum)`` are all-gathered and merged by
   log-sum-exp.  No K/V row ever crosses NVLink.
 * :func:`shard_rows` / :func:`shard_heads` — the partition arithmetic, shared with the tests.
@@ -75,7 +75,10 @@ class SequenceShardedStep:
 
     ``local_topk(q, k) -> (bits, gidx)``  int32/uint32-pattern tensors ``(P, k)``, padded with 0xFFFFFFFF
     ``merge(bits_all, gidx_all, k) -> sel``  ``(P, k)`` global row ids from ``(P, world*k)`` candidates
-    ``attend_owned(q, sel) -> (acc, ml)``  fp32 ``(P*G, D)`` and ``(P*G, 2)``
+    ``merge_count(bits_all, k, rank) -> count``  ``(P,)`` int32 from the gathered ``(world, P, k)`` keys: how many
+    leading entries of this rank's own list are among the global k best
+    ``attend_owned(q, ids, count=None) -> (acc, ml)``  fp32 ``(P*G, D)`` and ``(P*G, 2)`` over the owned rows of
+    ``ids`` (the first ``count[p]`` of them when given)
     ``combine_packed(parts, rows, D) -> out``  from ``(world, rows*D + rows*2)``: per rank the accumulators
     followed by the (max, sum) pairs
     """
@@ -95,21 +98,42 @@ class SequenceShardedStep:
         dist.all_gather_into_tensor(out, flat, group=self.group)
         return out.view((self.world,) + tuple(t.shape))
 
-    def step(self, q: torch.Tensor) -> torch.Tensor:
-        """Two exchanges per step: the candidates (one buffer holding bits and ids) and the partial
-        attention results (one buffer holding accumulators and (max, sum) pairs)."""
+    #: dc_merge_sorted_count keeps all ranks' lists in shared memory
+    PREFIX_MERGE_MAX_BYTES = 200 * 1024
+
+    def step(self, q: torch.Tensor, want_selection: bool = False) -> torch.Tensor:
+        """Two exchanges per step: the candidates and the partial attention results (one buffer holding
+        accumulators and (max, sum) pairs).
+
+        Every rank's candidate list is sorted, so the global winners a rank owns are a prefix of its own
+        list: only the ranking keys are exchanged, each rank computes the length of its prefix
+        (``merge_count``) and attends over it.  ``want_selection`` (and lists too long for that kernel)
+        also exchange the ids and run the full merge select, which leaves the global row list, identical
+        on all ranks, in ``last_selection``."""
         k = self.topk
-        bits, gidx = self.backend.local_topk(q, k)                       # (P, k) each
-        packed = _adjacent(bits, gidx)                                   # (2, P, k) without a copy when possible
-        cand = self._all_gather(packed)                                  # (world, 2, P, k)
+        bits, gidx = self.backend.local_topk(q, k)                       # (P, k) each, ascending, padded
         P = bits.shape[0]
-        cand = cand.permute(1, 2, 0, 3).reshape(2, P, self.world * k).contiguous()
-        sel = self.backend.merge(cand[0], cand[1], k)                    # (P, k) global ids, identical on all ranks
-        acc, ml = self.backend.attend_owned(q, sel)
+        use_prefix = self.world * k * 4 <= self.PREFIX_MERGE_MAX_BYTES and hasattr(self.backend, "merge_count")
+        sel = None
+        bits_all = None
+        if want_selection or not use_prefix:
+            packed = _adjacent(bits, gidx)                               # (2, P, k) without a copy when possible
+            cand = self._all_gather(packed)                              # (world, 2, P, k)
+            bits_all = cand[:, 0]
+            flat = cand.permute(1, 2, 0, 3).reshape(2, P, self.world * k).contiguous()
+            sel = self.backend.merge(flat[0], flat[1], k)                # (P, k) global ids
+            self.last_selection = sel
+        if use_prefix:
+            if bits_all is None:
+                bits_all = self._all_gather(bits)                        # (world, P, k)
+            count = self.backend.merge_count(bits_all.contiguous(), k, self.rank)   # (P,) int32
+            self.last_owned = (gidx, count)
+            acc, ml = self.backend.attend_owned(q, gidx, count)
+        else:
+            acc, ml = self.backend.attend_owned(q, sel)
         rows, D = acc.shape
         flat = _adjacent_flat(acc, ml)                                   # [acc | ml] as one flat buffer
         parts = self._all_gather(flat)                                   # (world, rows*D + rows*2)
-        self.last_selection = sel
         return self.backend.combine_packed(parts, rows, D)
 
 
@@ -155,13 +179,20 @@ class GpuShardBackend:
                                            sel.data_ptr(), k, self.status.data_ptr(), self._stream()))
         return sel
 
-    def attend_owned(self, q, sel):
+    def merge_count(self, bits_all, k, rank):
+        world = bits_all.shape[0]
+        count = self._buf("count", (self.P,), torch.int32)
+        _lib.check(self.lib.dc_merge_sorted_count(bits_all.data_ptr(), world, self.P, k, rank, count.data_ptr(),
+                                                  self._stream()))
+        return count
+
+    def attend_owned(self, q, sel, count=None):
         rows = self.P * self.G
         flat = self._buf("partial", (rows * (self.D + 2),), torch.float32)
         acc = flat[:rows * self.D].view(rows, self.D)
         ml = flat[rows * self.D:].view(rows, 2)
         self.e.attend_owned(q, sel, sel.shape[1], acc, ml, res_k=self.res_k, res_v=self.res_v, res_len=self.res_len,
-                            k_new=self.k_new, v_new=self.v_new, scale=self.scale)
+                            k_new=self.k_new, v_new=self.v_new, scale=self.scale, sel_count=count)
         return acc, ml
 
     def combine_packed(self, parts, rows, D):

@@ -224,12 +224,14 @@ int dc_local_topk(dc_engine* e, const void* q, int topk, uint32_t* out_bits,
  * neither sink nor window).  Writes un-normalised partial results:
  *   out_acc (bsz, q_heads, head_dim) fp32 = sum_j exp(s_j - m) v_j
  *   out_ml  (bsz, q_heads, 2) fp32 = (m in log2 units, l = sum_j exp2(s_j - m))
- * which dc_lse_combine merges.
+ * which dc_lse_combine merges.  sel_count (may be NULL): per problem, only the
+ * first sel_count[p] entries of its id list are attended (what
+ * dc_merge_sorted_count returns for this rank's own candidate list).
  */
 int dc_attend_owned(dc_engine* e, const void* q, const uint32_t* sel_gidx, int n_sel,
                     const void* k_new, const void* v_new, void* res_k, void* res_v,
                     int64_t res_stride_b, int64_t res_stride_h, int res_len, float scale,
-                    float* out_acc, float* out_ml, uint64_t stream);
+                    float* out_acc, float* out_ml, const int32_t* sel_count, uint64_t stream);
 
 /* ------------------------------------------------------------------------- *
  * Stateless kernels (device pointers only).  The engine calls are compositions
@@ -308,6 +310,22 @@ int dc_sparse_attend_noalloc(const void* k_store, const void* v_store, int64_t p
                              const void* k_new, const void* v_new, void* res_k, void* res_v,
                              int64_t res_stride_b, int64_t res_stride_h, int res_len, float scale,
                              void* out, float* out_lse, float* out_acc, float* out_ml, uint64_t stream);
+
+/*
+ * Merge of per-rank candidate lists for a sequence-sharded search, without
+ * moving row ids.  bits_all: (world, n_prob, k) uint32, the ascending ranking
+ * keys that dc_local_topk wrote on every rank (0xFFFFFFFF pads), as an
+ * all-gather delivers them.  Ranks own contiguous, ascending row ranges, so on
+ * equal keys a lower rank's rows come first (the reference's tie rule, smaller
+ * row id wins: nsw.rs:74-91,612).  The global k best that `my_rank` owns are a
+ * prefix of its own list; out_count[p] (int32, n_prob) receives its length, to
+ * be passed to dc_attend_owned as sel_count together with this rank's own id
+ * list.  Requires world * k * 4 bytes <= 200 KB (DC_EINVAL otherwise: merge
+ * (bits, id) pairs with dc_topk_select instead).  No counterpart in the
+ * reference, which is single-process.
+ */
+int dc_merge_sorted_count(const uint32_t* bits_all, int world, int n_prob, int k, int my_rank,
+                          int32_t* out_count, uint64_t stream);
 
 /*
  * Log-sum-exp merge of `n_part` partial results (split-K partials of one GPU, or

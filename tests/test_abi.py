@@ -47,6 +47,7 @@ def test_argument_validation_without_gpu():
     assert lib.dc_ctx_len(None, None) == -1
     assert lib.dc_score_scan(None, 0, 1, 1, 128, 0, None, 0, 1, None, 0, None, 0) == -1
     assert lib.dc_topk_select(None, None, 0, 1, 1, 1, None, None, None, 0, None, 0) == -1
+    assert lib.dc_merge_sorted_count(None, 2, 1, 8, 0, None, 0) == -1
 
 
 def test_unknown_engine_option_is_rejected():

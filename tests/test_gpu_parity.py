@@ -590,6 +590,35 @@ def test_kvcache_manager_flow(oracle_lib):
     assert cache.kvbuf_suffix_len == suffix + 1
 
 
+def test_merge_sorted_count_against_a_full_sort(lib):
+    """dc_merge_sorted_count on hand-made rank lists: heavy ties across ranks (resolved towards the lower
+    rank), pads, a rank with no rows, k not a multiple of 4, all winners on one rank."""
+    rng = np.random.default_rng(41)
+    for world, k, P, spread in ((2, 7, 3, 3), (3, 33, 2, 5), (8, 4096, 2, 2000), (8, 1024, 8, 50), (5, 600, 1, 1), (4, 2048, 2, 10 ** 6)):
+        lists = np.full((world, P, k), 0xFFFFFFFF, np.uint32)
+        for r in range(world):
+            for p in range(P):
+                m = int(rng.integers(0, k + 1)) if (r + p) % 3 else k       # some lists shorter than k (pads)
+                if r == 1 and p == 0:
+                    m = 0                                                     # a rank that holds no rows
+                vals = rng.integers(0x47000000, 0x47000000 + spread, m).astype(np.uint32)
+                if r == 0 and p == P - 1:
+                    vals = np.full(k, 0x46000000, np.uint32); m = k           # every winner on rank 0
+                lists[r, p, :m] = np.sort(vals)
+        dev = _dev(lists.view(np.int32))
+        for me in range(world):
+            out = torch.full((P,), -1, dtype=torch.int32, device="cuda")
+            rc = lib.dc_merge_sorted_count(dev.data_ptr(), world, P, k, me, out.data_ptr(), _stream())
+            assert rc == 0, lib.dc_last_error()
+            torch.cuda.synchronize()
+            for p in range(P):
+                keys = sorted((int(lists[r, p, i]), r, i) for r in range(world) for i in range(k)
+                              if lists[r, p, i] != 0xFFFFFFFF)[:k]
+                assert int(out[p]) == sum(1 for _, r, _ in keys if r == me), (world, k, p, me)
+    big = torch.zeros(8 * 16384, dtype=torch.int32, device="cuda")   # 512 KB of lists: refused, not truncated
+    assert lib.dc_merge_sorted_count(big.data_ptr(), 8, 1, 16384, 0, big.data_ptr(), _stream()) == -1
+
+
 def test_sequence_sharded_step_emulated_on_one_gpu(oracle_lib):
     """The sequence-sharded step with every rank's engine on this one GPU and the two all-gathers
     done by hand: local top-k with global ids and padding, merge select, attention over owned rows,
@@ -624,10 +653,23 @@ def test_sequence_sharded_step_emulated_on_one_gpu(oracle_lib):
     sels = [b.merge(cand[0], cand[1], topk).clone() for b in backends]
     assert all(torch.equal(sels[0], s) for s in sels)
     parts_out = [torch.cat([t.reshape(-1) for t in b.attend_owned(qd, sels[0])]) for b in backends]
-    out = backends[0].combine_packed(torch.stack(parts_out).contiguous(), P * G, D)
+    out = backends[0].combine_packed(torch.stack(parts_out).contiguous(), P * G, D).clone()
+    # the keys-only path: every rank counts the prefix of its own sorted list that is globally selected
+    bits_all = torch.stack([c[0] for c in cands]).contiguous()                                  # (world, P, k)
+    parts_fast = []
+    for r, b in enumerate(backends):
+        count = b.merge_count(bits_all, topk, r).clone()
+        own = cands[r][1].cpu().numpy().view(np.uint32)
+        start, length = parts[r]
+        for p in range(P):  # prefix of my list == the merged selection restricted to my rows
+            want = set(int(x) for x in sels[0][p].cpu().numpy().view(np.uint32) if start <= x < start + length)
+            assert set(int(x) for x in own[p][:int(count[p])]) == want
+        parts_fast.append(torch.cat([t.reshape(-1) for t in b.attend_owned(qd, cands[r][1].contiguous(), count)]))
+    out_fast = backends[0].combine_packed(torch.stack(parts_fast).contiguous(), P * G, D)
     for e in engines:
         e.check_status()
     torch.cuda.synchronize()
+    assert torch.equal(out_fast, out)
     ku, vu = util.u16(k).reshape(P, -1, D), util.u16(v).reshape(P, -1, D)
     ref = util.oracle_decode_step(
         oracle_lib, np.ascontiguousarray(ku[:, sink:sink + n_r]), np.ascontiguousarray(vu[:, sink:sink + n_r]),

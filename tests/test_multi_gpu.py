@@ -43,8 +43,10 @@ def _rank_main(rank, world, port, tmpdir):
             if rank == world - 1:
                 kn, vn = k[:, :, -1].contiguous().cuda(), v[:, :, -1].contiguous().cuda()
         step = sharded.SequenceShardedStep(sharded.GpuShardBackend(eng, start, res_k, res_v, rows, kn, vn), topk)
-        out = step.step(q).clone()
+        fast = step.step(q).clone()                          # keys-only exchange, prefix counts
+        out = step.step(q, want_selection=True).clone()      # also ids + the full merge select
         sel = step.last_selection.clone()
+        assert torch.equal(fast, out)
         eng.check_status()
         torch.cuda.synchronize()
         if rank == 0:  # single-GPU fused step on the whole sequence

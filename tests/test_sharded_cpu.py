@@ -54,9 +54,21 @@ class OracleShardBackend:
         sel = np.stack([self.o.topk(b[p], k, ids=g[p], method="sort")[1] for p in range(self.P)])
         return torch.from_numpy(sel.view(np.int32))
 
-    def attend_owned(self, q, sel):
+    def merge_count(self, bits_all, k, rank):
+        """Order all candidates by (key, rank, position), keep the first k valid ones, count this rank's."""
+        b = bits_all.numpy().view(np.uint32)                      # (world, P, k)
+        world = b.shape[0]
+        out = np.zeros(self.P, np.int32)
+        for p in range(self.P):
+            keys = [(int(b[r, p, i]), r, i) for r in range(world) for i in range(k) if b[r, p, i] != sharded.PAD]
+            out[p] = sum(1 for _, r, _ in sorted(keys)[:k] if r == rank)
+        return torch.from_numpy(out)
+
+    def attend_owned(self, q, sel, count=None):
         qf = self.o.to_f32(util.u16(q).reshape(self.P * self.G, self.D), 0).astype(np.float64)
         s_ids = sel.numpy().view(np.uint32).astype(np.int64)
+        if count is not None:
+            s_ids = [s_ids[p][:int(count[p])] for p in range(self.P)]
         acc = np.zeros((self.P * self.G, self.D), np.float32)
         ml = np.zeros((self.P * self.G, 2), np.float32)
         for p in range(self.P):
@@ -122,8 +134,14 @@ def _rank_main(rank, world, port, tmpdir):
             k_new, v_new = ku[:, -1], vu[:, -1]
         backend = OracleShardBackend(oracle, ks, vs, start, G, res_k, res_v, k_new, v_new, D ** -0.5)
         step = sharded.SequenceShardedStep(backend, topk)
-        out = step.step(q).numpy()
+        fast = step.step(q).numpy()                         # keys only: prefix counts
+        out = step.step(q, want_selection=True).numpy()     # also the full merge with ids
+        assert np.array_equal(fast, out)
         sel = step.last_selection.numpy().view(np.uint32)
+        gidx, count = step.last_owned
+        for p in range(P):                                  # my prefix = the selected rows in my range
+            mine = set(int(x) for x in gidx.numpy().view(np.uint32)[p][:int(count[p])])
+            assert mine == set(int(x) for x in sel[p] if start <= x < start + length)
         # unsharded reference
         ref = util.oracle_decode_step(
             oracle, np.ascontiguousarray(ku[:, sink:sink + n_r]), np.ascontiguousarray(vu[:, sink:sink + n_r]),

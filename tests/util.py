@@ -32,7 +32,7 @@ def ulp_of_dist(bits: np.ndarray) -> np.ndarray:
 
 
 def check_selection_parity(gpu_idx, oracle_idx, oracle_all_bits):
-    """BASELINE rule: the selected index SETS must match exactly, except for ties within one
+    """Parity rule of the task: the selected index SETS must match exactly, except for ties within one
     fp32 ulp of dist at the selection boundary.  `oracle_all_bits` are the oracle dist bits of
     every row.  Returns the number of boundary substitutions."""
     gs, os_ = set(int(i) for i in gpu_idx), set(int(i) for i in oracle_idx)

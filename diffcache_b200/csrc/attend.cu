@@ -290,11 +290,10 @@ sparse_attend_kernel(const AttendArgs a) {
     const unsigned xp = (x7 & 6u) << 4, lowp = (((lane >> 4) ^ x7) & 1u) << 4;             // chunk = 2*n2 + (lane>>4)
 
     for (int t = 0; t < n_tiles; t++) {
-        __syncthreads();  // tile t-1 fully consumed: its ring slot may be overwritten
+        cp_async_wait<NS - 2>();  // this thread's copies of tile t have landed (newer tiles may be in flight)
+        __syncthreads();          // ... and everyone's; everyone is also done with tile t-1, whose slot is reused now
         issue_tile(t + NS - 1, my_id);
         my_id = fetch_id(t + NS);
-        cp_async_wait<NS - 1>();
-        __syncthreads();  // every thread's copies of tile t have landed
 
         const unsigned ks = smem_base + (t % NS) * STAGE_BYTES;
         const unsigned vs = ks + TILE * D * 2;

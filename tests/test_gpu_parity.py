@@ -236,6 +236,13 @@ def test_engine_query_matches_reference_semantics(oracle_lib, dtype):
         assert np.array_equal(out_k[b, h], ku[b, h][out_i[b, h]])
         assert np.array_equal(out_v[b, h], vu[b, h][out_i[b, h]])
     assert subs <= P * 4, f"{subs} boundary substitutions is more than ulp ties explain"
+    # query_streaming (lib.rs:626-636): raw stream handle and device pointers; same answer on the device
+    dk = torch.zeros((B, Hkv, ef, D), dtype=torch.int16, device="cuda")
+    dv = torch.zeros_like(dk)
+    side = torch.cuda.Stream()
+    eng.query_streaming(side.cuda_stream, dk.data_ptr(), dv.data_ptr(), qm, ef)
+    side.synchronize()
+    assert np.array_equal(dk.cpu().numpy().view(np.uint16), out_k) and np.array_equal(dv.cpu().numpy().view(np.uint16), out_v)
     # the engine's keys, as float32 (get_keys, lib.rs:646-649)
     assert np.array_equal(eng.get_keys(), oracle_lib.to_f32(ku, dt))
     # ef beyond the store is clamped and the output shape follows (lib.rs:374,384-385)
@@ -588,6 +595,24 @@ def test_kvcache_manager_flow(oracle_lib):
         else:  # an ulp tie at the boundary: the fused path must still agree with the three-call path
             assert sum(same) >= P - 1
     assert cache.kvbuf_suffix_len == suffix + 1
+
+
+def test_gather_rows_stateless(lib):
+    """dc_gather_rows (nsw.rs:623-629): out[p][i] = store[p][ids[p][i]], 0xFFFFFFFF ids give zero rows."""
+    rng = np.random.default_rng(5)
+    for D in (64, 128, 256):
+        P, n, n_ids = 3, 500, 77
+        store = rng.integers(0, 65536, (P, n, D), dtype=np.uint16)
+        ids = rng.integers(0, n, (P, n_ids)).astype(np.uint32)
+        ids[:, ::9] = 0xFFFFFFFF
+        out = torch.full((P, n_ids, D), -1, dtype=torch.int16, device="cuda")
+        sd, idd = _dev(store.view(np.int16)), _dev(ids.view(np.int32))
+        rc = lib.dc_gather_rows(sd.data_ptr(), n * D, P, D, idd.data_ptr(), n_ids, n_ids, out.data_ptr(), _stream())
+        assert rc == 0, lib.dc_last_error()
+        torch.cuda.synchronize()
+        want = np.where((ids == 0xFFFFFFFF)[..., None], np.uint16(0),
+                        np.take_along_axis(store, np.minimum(ids, n - 1).astype(np.int64)[..., None], axis=1))
+        assert np.array_equal(out.cpu().numpy().view(np.uint16), want)
 
 
 def test_merge_sorted_count_against_a_full_sort(lib):

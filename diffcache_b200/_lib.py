@@ -27,6 +27,8 @@ SIGNATURES = {
     "dc_export_rows": (_i32, [_vp, _vp, _vp]),
     "dc_update_r_sq": (_i32, [_vp, _vp, _i32]),
     "dc_decode_attend": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i32, _i32, _f32, _vp, _vp, _vp, _u64]),
+    "dc_decode_attend_strided": (_i32, [_vp, _vp, _i64, _vp, _vp, _i64, _vp, _vp, _i64, _i64, _i32, _i32, _f32, _vp, _vp,
+                                        _vp, _u64]),
     "dc_set_adaptive_budget": (_i32, [_vp, _vp, _i32, _f32]),
     "dc_get_budget": (_i32, [_vp, _vp, _u64]),
     "dc_adaptive_budget": (_i32, [_vp, _i64, _i32, _i32, _i32, _vp, _i32, _f32, _vp, _u64]),

@@ -29,7 +29,9 @@ struct AttendArgs {
     int64_t n_rows;        // valid rows per problem in the store
     int kv_heads;
     int group;             // query heads per kv head
-    const uint16_t* q;     // (n_prob*group, D)
+    const uint16_t* q;     // (n_prob*group, D), or batches q_stride_b elements apart when q_stride_b != 0
+    int64_t q_stride_b;
+    int64_t new_stride_b;  // k_new / v_new: 0 = dense (n_prob, D), else elements between batches
     const uint32_t* sel;   // (n_prob, sel_stride) row ids, or nullptr
     int64_t sel_stride;
     int n_sel;
@@ -160,6 +162,7 @@ sparse_attend_kernel(const AttendArgs a) {
     __shared__ float s_ml[kAttWarps][kHeadsPerCta][2];
 
     const int has_new = a.k_new != nullptr ? 1 : 0;
+    const int64_t new_off = a.new_stride_b ? b * a.new_stride_b + static_cast<int64_t>(h) * D : prob * D;
     const int total = a.n_sel + a.res_len + has_new;
     const int per = (total + a.n_split - 1) / a.n_split;
     const int j0 = min(total, split * per);
@@ -169,7 +172,8 @@ sparse_attend_kernel(const AttendArgs a) {
     // A fragments of Q for every k-step: rows = heads of this chunk (zero beyond), raw 16-bit pairs
     uint32_t qa[KSTEPS][2];
     {
-        const uint16_t* qrow = a.q + (prob * a.group + g0 + gq) * D;
+        const uint16_t* qrow = a.q_stride_b ? a.q + b * a.q_stride_b + (static_cast<int64_t>(h) * a.group + g0 + gq) * D
+                                            : a.q + (prob * a.group + g0 + gq) * D;
 #pragma unroll
         for (int ks = 0; ks < KSTEPS; ks++) {
             qa[ks][0] = gq < n_heads ? *reinterpret_cast<const uint32_t*>(qrow + 16 * ks + 2 * tq) : 0u;
@@ -187,9 +191,9 @@ sparse_attend_kernel(const AttendArgs a) {
     // flash-attn's in-place append of the new token (base.py:134-142): one CTA per problem
     if (has_new && split == 0 && blockIdx.z == 0 && rk != nullptr && tid < LPR) {
         reinterpret_cast<uint4*>(rk + static_cast<int64_t>(a.res_len) * D)[tid] =
-            reinterpret_cast<const uint4*>(a.k_new + prob * D)[tid];
+            reinterpret_cast<const uint4*>(a.k_new + new_off)[tid];
         reinterpret_cast<uint4*>(rv + static_cast<int64_t>(a.res_len) * D)[tid] =
-            reinterpret_cast<const uint4*>(a.v_new + prob * D)[tid];
+            reinterpret_cast<const uint4*>(a.v_new + new_off)[tid];
     }
 
     // Row id of ONE of the NCOPY rows this lane group copies in tile `t`: lane `col` (< NCOPY) of a group
@@ -250,7 +254,7 @@ sparse_attend_kernel(const AttendArgs a) {
                             const int64_t row = j - a.n_sel;
                             kp = rk + row * D; vp = rv + row * D;
                         } else {
-                            kp = a.k_new + prob * D; vp = a.v_new + prob * D;
+                            kp = a.k_new + new_off; vp = a.v_new + new_off;
                         }
                     }
                     const bool ok = kp != nullptr;
@@ -575,8 +579,9 @@ int sparse_attend(const void* k_store, const void* v_store, int64_t prob_stride,
                   int64_t sel_stride, int n_sel, int64_t sel_base, const void* k_new, const void* v_new, void* res_k,
                   void* res_v, int64_t res_stride_b, int64_t res_stride_h, int res_len, float scale, void* out,
                   float* out_lse, float* out_acc, float* out_ml, void* scratch, cudaStream_t stream,
-                  const int32_t* sel_count) {
+                  const int32_t* sel_count, int64_t q_stride_b, int64_t new_stride_b) {
     DC_REQUIRE(q != nullptr && scratch != nullptr, "sparse_attend: null q/scratch");
+    DC_REQUIRE(q_stride_b % 8 == 0 && new_stride_b % 8 == 0, "sparse_attend: batch strides must be multiples of 8 elements");
     DC_REQUIRE(dtype == DC_BF16 || dtype == DC_FP16, "sparse_attend: dtype %d not supported", dtype);
     DC_REQUIRE(head_dim == 64 || head_dim == 128 || head_dim == 256, "sparse_attend: head_dim %d not in {64,128,256}",
                head_dim);
@@ -607,6 +612,8 @@ int sparse_attend(const void* k_store, const void* v_store, int64_t prob_stride,
     a.kv_heads = kv_heads;
     a.group = group;
     a.q = static_cast<const uint16_t*>(q);
+    a.q_stride_b = q_stride_b;
+    a.new_stride_b = new_stride_b;
     a.sel = sel;
     a.sel_stride = sel_stride;
     a.n_sel = n_sel;
@@ -716,5 +723,5 @@ extern "C" int dc_sparse_attend_noalloc(const void* k_store, const void* v_store
     if (rc != DC_OK) return rc;
     return sparse_attend(k_store, v_store, prob_stride, n_rows, n_prob, kv_heads, group, head_dim, dtype, q, sel,
                          sel_stride, n_sel, sel_base, k_new, v_new, res_k, res_v, res_stride_b, res_stride_h, res_len,
-                         scale, out, out_lse, out_acc, out_ml, scratch, as_stream(stream), nullptr);
+                         scale, out, out_lse, out_acc, out_ml, scratch, as_stream(stream), nullptr, 0, 0);
 }

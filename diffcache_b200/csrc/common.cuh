@@ -97,21 +97,32 @@ __device__ __forceinline__ Wide32 ld_stream32(const void* p) {
 }
 
 // Eight query elements [col0, col0+8) of the retrieval query of one problem as fp32.
-// q_mode 0: q already holds the group mean.  q_mode 1: q holds the `group` query heads of
+// Where the query rows of problem `prob` (= batch * kv_heads + kv head) start.
+// q_mode 0: q holds one group-mean row per problem, densely.  q_mode 1: q holds the `group` query heads of
+// every problem back to back; q_stride_b == 0 means the batches are dense too ((n_prob*group, dim)),
+// otherwise q_stride_b elements separate two batches (a slice of a fused q/k/v projection output).
+__device__ __forceinline__ const uint16_t* query_base(const uint16_t* q, int64_t prob, int dim, int q_mode, int group,
+                                                     int kv_heads, int64_t q_stride_b) {
+    if (q_mode == 0) return q + prob * dim;
+    if (q_stride_b == 0) return q + prob * group * dim;
+    return q + (prob / kv_heads) * q_stride_b + (prob % kv_heads) * group * dim;
+}
+
+// q_mode 0: qbase already holds the group mean.  q_mode 1: qbase holds the `group` query heads of
 // the problem back to back; the mean is the fp32 sum in head order times 1/group, rounded
 // once to the element type (what torch's mean over a bf16 tensor produces).
 template <int DT>
-__device__ __forceinline__ void load_query8(const uint16_t* q, int64_t prob, int dim, int q_mode, int group,
-                                            int col0, float (&out)[8]) {
+__device__ __forceinline__ void load_query8(const uint16_t* qbase, int dim, int q_mode, int group, int col0,
+                                            float (&out)[8]) {
     if (q_mode == 0) {
-        uint4 w = *reinterpret_cast<const uint4*>(q + prob * dim + col0);
+        uint4 w = *reinterpret_cast<const uint4*>(qbase + col0);
         unpack8<DT>(w, out);
     } else {
         float s[8];
 #pragma unroll
         for (int j = 0; j < 8; j++) s[j] = 0.0f;
         for (int g = 0; g < group; g++) {
-            uint4 w = *reinterpret_cast<const uint4*>(q + (prob * group + g) * dim + col0);
+            uint4 w = *reinterpret_cast<const uint4*>(qbase + g * dim + col0);
             float f[8];
             unpack8<DT>(w, f);
 #pragma unroll

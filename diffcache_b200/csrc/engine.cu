@@ -18,7 +18,7 @@ namespace dc {
 // ---- kernels defined in the other translation units ----
 int score_scan(const void* keys, int64_t prob_stride, int n_prob, int64_t n, int head_dim, int dtype, const void* q,
                int q_mode, int group, uint32_t* scores, int64_t score_stride, uint32_t* minmax, cudaStream_t stream,
-               uint32_t* status = nullptr);
+               uint32_t* status = nullptr, int kv_heads = 1, int64_t q_stride_b = 0);
 int topk_select(const uint32_t* bits, const uint32_t* ids, int64_t in_stride, int n_prob, int64_t n, int k,
                 const uint32_t* minmax, uint32_t id_offset, uint32_t* out_bits, uint32_t* out_ids, int64_t out_stride,
                 uint32_t* status, cudaStream_t stream, uint32_t* minmax_reset = nullptr);
@@ -31,7 +31,7 @@ int sparse_attend(const void* k_store, const void* v_store, int64_t prob_stride,
                   int64_t sel_stride, int n_sel, int64_t sel_base, const void* k_new, const void* v_new, void* res_k,
                   void* res_v, int64_t res_stride_b, int64_t res_stride_h, int res_len, float scale, void* out,
                   float* out_lse, float* out_acc, float* out_ml, void* scratch, cudaStream_t stream,
-                  const int32_t* sel_count = nullptr);
+                  const int32_t* sel_count = nullptr, int64_t q_stride_b = 0, int64_t new_stride_b = 0);
 int adaptive_budget(const uint32_t* bits, int64_t stride, int n_prob, int k, int head_dim, const int* seq, int n_seq,
                     float threshold, int32_t* budget, cudaStream_t stream);
 int64_t attend_scratch_bytes(int n_prob, int group, int head_dim);
@@ -197,11 +197,11 @@ int gather_rows(const void* store, int64_t prob_stride, int n_prob, int dim, con
 // scan + select on the engine's own buffers; leaves (bits, ids) of the k best rows per problem in
 // out_bits/out_ids (row stride k).  q: device pointer, q_mode as in dc_score_scan.
 int scan_and_select(dc_engine* e, const void* q, int q_mode, int k, uint32_t id_offset, uint32_t* out_bits,
-                    uint32_t* out_ids, cudaStream_t s, cudaEvent_t* ev = nullptr) {
+                    uint32_t* out_ids, cudaStream_t s, cudaEvent_t* ev = nullptr, int64_t q_stride_b = 0) {
     // e->minmax is in its initial state here: set once in dc_create, and put back by every select
     if (ev) DC_CUDA_TRY(cudaEventRecord(ev[0], s));
     int rc = score_scan(e->k, e->prob_stride, e->n_prob, e->ctx_len, e->head_dim, e->dtype, q, q_mode, e->group, e->scores,
-                    e->score_stride, e->minmax, s, e->status);
+                    e->score_stride, e->minmax, s, e->status, e->kv_heads, q_stride_b);
     if (rc) return rc;
     if (ev) DC_CUDA_TRY(cudaEventRecord(ev[1], s));
     rc = topk_select(e->scores, nullptr, e->score_stride, e->n_prob, e->ctx_len, k, e->minmax, id_offset, out_bits,
@@ -480,8 +480,22 @@ int dc_update_r_sq(dc_engine* e, const float* r_sq, int n) {
 int dc_decode_attend(dc_engine* e, const void* q, const void* k_new, const void* v_new, void* res_k, void* res_v,
                      int64_t res_stride_b, int64_t res_stride_h, int res_len, int topk, float scale, void* out,
                      int32_t* out_idx, float* out_lse, uint64_t stream) {
+    return dc_decode_attend_strided(e, q, 0, k_new, v_new, 0, res_k, res_v, res_stride_b, res_stride_h, res_len, topk,
+                                    scale, out, out_idx, out_lse, stream);
+}
+
+int dc_decode_attend_strided(dc_engine* e, const void* q, int64_t q_stride_b, const void* k_new, const void* v_new,
+                             int64_t new_stride_b, void* res_k, void* res_v, int64_t res_stride_b,
+                             int64_t res_stride_h, int res_len, int topk, float scale, void* out, int32_t* out_idx,
+                             float* out_lse, uint64_t stream) {
     DC_ENGINE_ENTER(e);
     DC_REQUIRE(q && out, "dc_decode_attend: null q/out");
+    DC_REQUIRE(q_stride_b >= 0 && new_stride_b >= 0 && q_stride_b % 8 == 0 && new_stride_b % 8 == 0,
+               "dc_decode_attend: batch strides must be non-negative multiples of 8 elements");
+    DC_REQUIRE(q_stride_b == 0 || q_stride_b >= static_cast<int64_t>(e->q_heads) * e->head_dim,
+               "dc_decode_attend: q batch stride smaller than one batch of query heads");
+    DC_REQUIRE(new_stride_b == 0 || new_stride_b >= static_cast<int64_t>(e->kv_heads) * e->head_dim,
+               "dc_decode_attend: k_new/v_new batch stride smaller than one batch of kv heads");
     DC_REQUIRE(topk >= 0, "dc_decode_attend: negative topk");
     const int k = static_cast<int>(std::min<int64_t>(topk, e->ctx_len));
     DC_REQUIRE(k <= DC_MAX_TOPK, "dc_decode_attend: topk=%d exceeds DC_MAX_TOPK=%d", k, DC_MAX_TOPK);
@@ -491,7 +505,7 @@ int dc_decode_attend(dc_engine* e, const void* q, const void* k_new, const void*
     cudaEvent_t* ev = nullptr;
     if (k > 0 && e->phase_count < e->phase_cap) ev = &e->phase_events[4 * e->phase_count];
     if (k > 0) {
-        rc = scan_and_select(e, q, 1, k, 0u, e->sel_bits, e->sel_idx, s, ev);
+        rc = scan_and_select(e, q, 1, k, 0u, e->sel_bits, e->sel_idx, s, ev, q_stride_b);
         if (rc) return rc;
     }
     const int32_t* sel_count = nullptr;
@@ -503,7 +517,7 @@ int dc_decode_attend(dc_engine* e, const void* q, const void* k_new, const void*
     }
     rc = sparse_attend(e->k, e->v, e->prob_stride, e->ctx_len, e->n_prob, e->kv_heads, e->group, e->head_dim, e->dtype,
                        q, e->sel_idx, k, k, 0, k_new, v_new, res_k, res_v, res_stride_b, res_stride_h, res_len, scale,
-                       out, out_lse, nullptr, nullptr, e->att_scratch, s, sel_count);
+                       out, out_lse, nullptr, nullptr, e->att_scratch, s, sel_count, q_stride_b, new_stride_b);
     if (rc) return rc;
     if (ev) {
         DC_CUDA_TRY(cudaEventRecord(ev[3], s));

@@ -105,7 +105,7 @@ __global__ void rerank_kernel(const uint16_t* __restrict__ keys, int64_t prob_st
     const int col = lane % LPR, sub = lane / LPR;
     const int64_t prob = blockIdx.y;
     float qv[8];
-    load_query8<DT>(q, prob, D, q_mode, group, col * 8, qv);
+    load_query8<DT>(query_base(q, prob, D, q_mode, group, 1, 0), D, q_mode, group, col * 8, qv);
     const int warps = blockDim.x / 32;
     const int tile0 = (blockIdx.x * warps + warp) * (NL * R);
     if (tile0 >= n_ids) return;

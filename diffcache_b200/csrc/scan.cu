@@ -32,8 +32,8 @@ constexpr int kLoadsPerTile = 8;  // 16-byte loads in flight per lane
 template <int DT, int LPR>
 __global__ void __launch_bounds__(kScanThreads)
 score_scan_kernel(const uint16_t* __restrict__ keys, int64_t prob_stride, int64_t n, const uint16_t* __restrict__ q,
-                  int q_mode, int group, uint32_t* __restrict__ scores, int64_t score_stride,
-                  uint32_t* __restrict__ minmax, int rows_per_cta) {
+                  int q_mode, int group, int kv_heads, int64_t q_stride_b, uint32_t* __restrict__ scores,
+                  int64_t score_stride, uint32_t* __restrict__ minmax, int rows_per_cta) {
     constexpr int D = LPR * 8;
     constexpr int R = 32 / LPR;               // rows covered by one warp-wide load
     constexpr int TR = kLoadsPerTile * R;     // rows per warp tile
@@ -44,7 +44,7 @@ score_scan_kernel(const uint16_t* __restrict__ keys, int64_t prob_stride, int64_
     const int64_t prob = blockIdx.y;
 
     float qv[8];
-    load_query8<DT>(q, prob, D, q_mode, group, col * 8, qv);
+    load_query8<DT>(query_base(q, prob, D, q_mode, group, kv_heads, q_stride_b), D, q_mode, group, col * 8, qv);
 
     const uint16_t* kp = keys + prob * prob_stride + col * 8;
     uint32_t* sp = scores + prob * score_stride;
@@ -109,8 +109,8 @@ score_scan_kernel(const uint16_t* __restrict__ keys, int64_t prob_stride, int64_
 template <int DT, int LW>
 __global__ void __launch_bounds__(kScanThreads)
 score_scan_wide_kernel(const uint16_t* __restrict__ keys, int64_t prob_stride, int64_t n, const uint16_t* __restrict__ q,
-                       int q_mode, int group, uint32_t* __restrict__ scores, int64_t score_stride,
-                       uint32_t* __restrict__ minmax, int rows_per_cta) {
+                       int q_mode, int group, int kv_heads, int64_t q_stride_b, uint32_t* __restrict__ scores,
+                       int64_t score_stride, uint32_t* __restrict__ minmax, int rows_per_cta) {
     constexpr int D = LW * 16;
     constexpr int R = 32 / LW;
     constexpr int TR = kLoadsPerTile * R;
@@ -123,8 +123,9 @@ score_scan_wide_kernel(const uint16_t* __restrict__ keys, int64_t prob_stride, i
     float qv[16];
     {
         float a[8], b[8];
-        load_query8<DT>(q, prob, D, q_mode, group, col * 16, a);
-        load_query8<DT>(q, prob, D, q_mode, group, col * 16 + 8, b);
+        const uint16_t* qb = query_base(q, prob, D, q_mode, group, kv_heads, q_stride_b);
+        load_query8<DT>(qb, D, q_mode, group, col * 16, a);
+        load_query8<DT>(qb, D, q_mode, group, col * 16 + 8, b);
 #pragma unroll
         for (int j = 0; j < 8; j++) { qv[j] = a[j]; qv[8 + j] = b[j]; }
     }
@@ -205,9 +206,9 @@ __device__ __forceinline__ void mbar_arrive(unsigned long long* bar) {
 template <int DT, int LPR>
 __global__ void __launch_bounds__(kTmaThreads, 1)
 score_scan_tma_kernel(const uint16_t* __restrict__ keys, int64_t prob_stride, int64_t n, int n_prob,
-                      const uint16_t* __restrict__ q, int q_mode, int group, uint32_t* __restrict__ scores,
-                      int64_t score_stride, uint32_t* __restrict__ minmax, uint32_t* __restrict__ status,
-                      int q_table) {
+                      const uint16_t* __restrict__ q, int q_mode, int group, int kv_heads, int64_t q_stride_b,
+                      uint32_t* __restrict__ scores, int64_t score_stride, uint32_t* __restrict__ minmax,
+                      uint32_t* __restrict__ status, int q_table) {
     constexpr int D = LPR * 8;
     constexpr int R = 32 / LPR;
     constexpr int TR = kLoadsPerTile * R;
@@ -228,7 +229,8 @@ score_scan_tma_kernel(const uint16_t* __restrict__ keys, int64_t prob_stride, in
     if (q_table) {
         for (int i = threadIdx.x; i < n_prob * LPR; i += kTmaThreads) {
             float f[8];
-            load_query8<DT>(q, i / LPR, D, q_mode, group, (i % LPR) * 8, f);
+            load_query8<DT>(query_base(q, i / LPR, D, q_mode, group, kv_heads, q_stride_b), D, q_mode, group,
+                            (i % LPR) * 8, f);
             uint4 w;
             w.x = float_to_elem<DT>(f[0]) | (static_cast<uint32_t>(float_to_elem<DT>(f[1])) << 16);
             w.y = float_to_elem<DT>(f[2]) | (static_cast<uint32_t>(float_to_elem<DT>(f[3])) << 16);
@@ -286,7 +288,7 @@ score_scan_tma_kernel(const uint16_t* __restrict__ keys, int64_t prob_stride, in
             if (cur_p >= 0) flush_minmax();
             cur_p = p;
             if (q_table) unpack8<DT>(*reinterpret_cast<const uint4*>(s_q + (p * LPR + col) * 8), qv);
-            else load_query8<DT>(q, p, D, q_mode, group, col * 8, qv);
+            else load_query8<DT>(query_base(q, p, D, q_mode, group, kv_heads, q_stride_b), D, q_mode, group, col * 8, qv);
         }
         // warp-uniform outcome: either every lane saw the stage arrive or the whole warp gives up
         if (!__all_sync(0xFFFFFFFFu, mbar_wait_bounded(&full[s], static_cast<unsigned>((it / kTmaStages) & 1)))) {
@@ -343,7 +345,7 @@ int env_int(const char* name, int dflt) {
 
 template <int DT, int LPR>
 int launch_scan(const void* keys, int64_t prob_stride, int n_prob, int64_t n, const void* q, int q_mode, int group,
-                uint32_t* scores, int64_t score_stride, uint32_t* minmax, uint32_t* status, cudaStream_t stream) {
+                int kv_heads, int64_t q_stride_b, uint32_t* scores, int64_t score_stride, uint32_t* minmax, uint32_t* status, cudaStream_t stream) {
     constexpr int TR = kLoadsPerTile * (32 / LPR);
     static int rows_cfg = env_int("DC_SCAN_ROWS_PER_CTA", 1024);
     int rows_per_cta = ((rows_cfg + kScanWarps * TR - 1) / (kScanWarps * TR)) * (kScanWarps * TR);
@@ -367,21 +369,21 @@ int launch_scan(const void* keys, int64_t prob_stride, int n_prob, int64_t n, co
         const int q_table = table_bytes <= static_cast<size_t>(kQTableMax) ? 1 : 0;
         score_scan_tma_kernel<DT, LPR><<<sm_count(), kTmaThreads, kRing + (q_table ? table_bytes : 0), stream>>>(
             static_cast<const uint16_t*>(keys), prob_stride, n, n_prob, static_cast<const uint16_t*>(q), q_mode, group,
-            scores, score_stride, minmax, status, q_table);
+            kv_heads, q_stride_b, scores, score_stride, minmax, status, q_table);
         DC_CUDA_TRY(cudaGetLastError());
         return DC_OK;
     }
     if (!want_narrow && LPR >= 8 && prob_stride % 16 == 0 && (reinterpret_cast<uintptr_t>(keys) & 31) == 0) {
         // rows_per_cta is a multiple of 8 warps x 8 loads x (32 / (LPR/2)) rows as well (LPR >= 8)
         score_scan_wide_kernel<DT, LPR / 2><<<grid, kScanThreads, 0, stream>>>(
-            static_cast<const uint16_t*>(keys), prob_stride, n, static_cast<const uint16_t*>(q), q_mode, group, scores,
-            score_stride, minmax, rows_per_cta);
+            static_cast<const uint16_t*>(keys), prob_stride, n, static_cast<const uint16_t*>(q), q_mode, group, kv_heads,
+            q_stride_b, scores, score_stride, minmax, rows_per_cta);
         DC_CUDA_TRY(cudaGetLastError());
         return DC_OK;
     }
     score_scan_kernel<DT, LPR><<<grid, kScanThreads, 0, stream>>>(
-        static_cast<const uint16_t*>(keys), prob_stride, n, static_cast<const uint16_t*>(q), q_mode, group, scores,
-        score_stride, minmax, rows_per_cta);
+        static_cast<const uint16_t*>(keys), prob_stride, n, static_cast<const uint16_t*>(q), q_mode, group, kv_heads,
+        q_stride_b, scores, score_stride, minmax, rows_per_cta);
     DC_CUDA_TRY(cudaGetLastError());
     return DC_OK;
 }
@@ -390,7 +392,7 @@ int launch_scan(const void* keys, int64_t prob_stride, int n_prob, int64_t n, co
 
 int score_scan(const void* keys, int64_t prob_stride, int n_prob, int64_t n, int head_dim, int dtype, const void* q,
                int q_mode, int group, uint32_t* scores, int64_t score_stride, uint32_t* minmax, cudaStream_t stream,
-               uint32_t* status) {
+               uint32_t* status, int kv_heads, int64_t q_stride_b) {
     DC_REQUIRE(keys && q && scores, "score_scan: null pointer");
     DC_REQUIRE(dtype == DC_BF16 || dtype == DC_FP16, "score_scan: dtype %d not supported", dtype);
     DC_REQUIRE(head_dim == 64 || head_dim == 128 || head_dim == 256, "score_scan: head_dim %d not in {64,128,256}",
@@ -398,13 +400,16 @@ int score_scan(const void* keys, int64_t prob_stride, int n_prob, int64_t n, int
     DC_REQUIRE(n_prob >= 0 && n_prob <= 65535 && n >= 0, "score_scan: bad sizes n_prob=%d n=%lld", n_prob,
                static_cast<long long>(n));
     DC_REQUIRE(q_mode == 0 || (q_mode == 1 && group >= 1), "score_scan: bad q_mode/group");
+    DC_REQUIRE(q_stride_b == 0 || (q_mode == 1 && kv_heads >= 1 && n_prob % kv_heads == 0 && q_stride_b % 8 == 0),
+               "score_scan: a batch stride needs q_mode 1, kv_heads dividing n_prob and a multiple of 8 elements");
+    if (kv_heads < 1) kv_heads = 1;
     DC_REQUIRE(prob_stride % 8 == 0 && (reinterpret_cast<uintptr_t>(keys) & 15) == 0 &&
                    (reinterpret_cast<uintptr_t>(q) & 15) == 0,
                "score_scan: keys/q must be 16-byte aligned and prob_stride a multiple of 8 elements");
     if (n_prob == 0 || n == 0) return DC_OK;
 #define DC_SCAN_CASE(DT, LPR) \
-    return launch_scan<DT, LPR>(keys, prob_stride, n_prob, n, q, q_mode, group, scores, score_stride, minmax, status, \
-                                stream)
+    return launch_scan<DT, LPR>(keys, prob_stride, n_prob, n, q, q_mode, group, kv_heads, q_stride_b, scores, \
+                                score_stride, minmax, status, stream)
     if (dtype == DC_BF16) {
         if (head_dim == 64) DC_SCAN_CASE(DC_BF16, 8);
         if (head_dim == 128) DC_SCAN_CASE(DC_BF16, 16);

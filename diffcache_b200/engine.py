@@ -255,16 +255,34 @@ class DiffCacheGPU:
 
         ``q``/``out`` ``(bsz, q_head_num, head_dim)``; ``res_k/res_v`` a view
         ``(bsz, kv_head_num, rows, head_dim)`` of the resident sink+window buffer whose first
-        ``res_len`` rows are valid; ``k_new/v_new`` ``(bsz, kv_head_num, head_dim)``."""
+        ``res_len`` rows are valid; ``k_new/v_new`` ``(bsz, kv_head_num, head_dim)``.  ``q``, ``k_new`` and
+        ``v_new`` may be slices of a fused projection output: heads dense inside a batch, any batch stride
+        (``k_new`` and ``v_new`` the same one)."""
+        qsb = self._batch_stride(q, self.q_head_num, "q")
+        nsb = 0
+        if k_new is not None:
+            nsb = self._batch_stride(k_new, self.kv_head_num, "k_new")
+            if self._batch_stride(v_new, self.kv_head_num, "v_new") != nsb:
+                raise ValueError("k_new and v_new must have the same batch stride")
         sb = sh = 0
         if res_k is not None:
             st = tuple(res_k.stride())
             if st != tuple(res_v.stride()) or st[3] != 1 or st[2] != self.head_dim:
                 raise ValueError("res_k/res_v must share strides with contiguous rows of head_dim")
             sb, sh = st[0], st[1]
-        _lib.check(self._lib.dc_decode_attend(self._h, _ptr(q), _ptr(k_new), _ptr(v_new), _ptr(res_k), _ptr(res_v), sb,
-                                              sh, int(res_len), int(topk), float(scale), _ptr(out), _ptr(out_idx),
-                                              _ptr(out_lse), _current_stream(stream)))
+        _lib.check(self._lib.dc_decode_attend_strided(self._h, _ptr(q), qsb, _ptr(k_new), _ptr(v_new), nsb, _ptr(res_k),
+                                                      _ptr(res_v), sb, sh, int(res_len), int(topk), float(scale),
+                                                      _ptr(out), _ptr(out_idx), _ptr(out_lse), _current_stream(stream)))
+
+    def _batch_stride(self, t, heads: int, what: str) -> int:
+        """0 for a dense ``(bsz, heads, head_dim)`` tensor, else its batch stride in elements."""
+        if not hasattr(t, "stride"):   # not a torch tensor: taken as dense
+            return 0
+        st, shape = tuple(t.stride()), tuple(t.shape)
+        # the stride of a dimension of size 1 is never used and may hold anything
+        if len(st) != 3 or (shape[2] != 1 and st[2] != 1) or (shape[1] != 1 and st[1] != self.head_dim):
+            raise ValueError(f"{what} must be (bsz, {heads}, head_dim) with dense heads; strides {st}")
+        return 0 if shape[0] == 1 or st[0] == heads * self.head_dim else int(st[0])
 
     def set_adaptive_budget(self, k_check_seq, attn_mass_threshold: float) -> None:
         """Switch the k-check on for ``decode_attend`` (``k_check_seq`` empty switches it off): per

@@ -88,9 +88,10 @@ class AttentionStack:
         for layer in range(self.n_layers):
             h = F.rms_norm(x, (self.hidden,), self.norm_w[layer], 1e-5)
             qkv = F.linear(h, self.wqkv[layer])
-            q = qkv[:, :nq].contiguous().view(B, self.q_local, D)
-            kn = qkv[:, nq:nq + nkv].contiguous().view(B, self.kv_local, D)
-            vn = qkv[:, nq + nkv:].contiguous().view(B, self.kv_local, D)
+            # slices of the fused projection output, passed as they are (batch stride = nq + 2*nkv)
+            q = qkv[:, :nq].unflatten(1, (self.q_local, D))
+            kn = qkv[:, nq:nq + nkv].unflatten(1, (self.kv_local, D))
+            vn = qkv[:, nq + nkv:].unflatten(1, (self.kv_local, D))
             self.engines[layer].decode_attend(q, self.attn_local, self.topk, res_k=self.res_k[layer],
                                               res_v=self.res_v[layer], res_len=self.res_rows, k_new=kn, v_new=vn)
             if self.world > 1:

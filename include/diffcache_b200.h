@@ -175,6 +175,17 @@ int dc_decode_attend(dc_engine* e, const void* q, const void* k_new, const void*
                      float* out_lse, uint64_t stream);
 
 /*
+ * dc_decode_attend for inputs that are slices of a fused q/k/v projection output (what a model's
+ * attention block holds at this point, src/diffcache/llama.py:181-195): inside a batch the heads are
+ * dense, but q_stride_b (new_stride_b) elements separate two batches of q (of k_new and v_new, which
+ * must share it).  0 means dense, i.e. dc_decode_attend.  Strides are multiples of 8 elements.
+ */
+int dc_decode_attend_strided(dc_engine* e, const void* q, int64_t q_stride_b, const void* k_new,
+                             const void* v_new, int64_t new_stride_b, void* res_k, void* res_v,
+                             int64_t res_stride_b, int64_t res_stride_h, int res_len, int topk, float scale,
+                             void* out, int32_t* out_idx, float* out_lse, uint64_t stream);
+
+/*
  * Adaptive retrieval budget.  Replaces the k-check early stop of the reference's
  * search (fit_alpha_from_logits / estimate_top_h_mass / k_check_early_stoppable,
  * diffcache_cpu/src/nsw.rs:198-300, applied at the checkpoints of `k_check_seq`,

@@ -458,6 +458,53 @@ def test_fused_step_replayed_from_a_cuda_graph():
     eng.close()
 
 
+@pytest.mark.parametrize("dtype,G,D", [("bf16", 4, 128), ("fp16", 2, 64), ("bf16", 16, 128)])
+def test_fused_step_accepts_fused_projection_slices(dtype, G, D):
+    """q, k_new and v_new given as slices of one (batch, (Hq + 2 Hkv) * D) projection output — heads dense
+    inside a batch, batches a row of that matrix apart — must give bit for bit what dense copies give,
+    scan variants included (the group-mean query is formed from the strided heads)."""
+    from diffcache_b200 import DiffCacheGPU
+
+    B, Hkv, n, topk, res_rows = 3, 2, 3000, 256, 40
+    tdt = torch.bfloat16 if dtype == "bf16" else torch.float16
+    k, v, _ = util.small_problem(B, Hkv, G, n + res_rows, D, seed=61, dtype=dtype)
+    eng = DiffCacheGPU(B, Hkv * G, Hkv, D, max_ctx_len=n, dtype=dtype)
+    eng.prefill(k[:, :, :n].contiguous().cuda().view(torch.uint16), v[:, :, :n].contiguous().cuda().view(torch.uint16))
+    nq, nkv = Hkv * G * D, Hkv * D
+    gen = torch.Generator().manual_seed(62)
+    qkv = torch.randn(B, nq + 2 * nkv + 24, generator=gen).to(tdt).cuda()      # + 24: a stride that is no multiple of D
+    q = qkv[:, :nq].unflatten(1, (Hkv * G, D))
+    kn = qkv[:, nq:nq + nkv].unflatten(1, (Hkv, D))
+    vn = qkv[:, nq + nkv:nq + 2 * nkv].unflatten(1, (Hkv, D))
+    assert not q.is_contiguous() and not kn.is_contiguous()
+
+    def run(qq, kk, vv, variant):
+        rk = torch.zeros((B, Hkv, res_rows + 4, D), dtype=tdt, device="cuda")
+        rv = torch.zeros_like(rk)
+        rk[:, :, :res_rows] = k[:, :, n:].cuda(); rv[:, :, :res_rows] = v[:, :, n:].cuda()
+        out = torch.empty((B, Hkv * G, D), dtype=tdt, device="cuda")
+        idx = torch.zeros((B, Hkv, topk), dtype=torch.int32, device="cuda")
+        eng.decode_attend(qq, out, topk, res_k=rk, res_v=rv, res_len=res_rows, k_new=kk, v_new=vv, out_idx=idx)
+        eng.check_status()
+        torch.cuda.synchronize()
+        return out, idx, rk[:, :, res_rows].clone(), rv[:, :, res_rows].clone()
+
+    import os
+    for variant in ("wide", "narrow", "tma"):
+        os.environ["DC_SCAN_VARIANT"] = variant
+        try:
+            dense = run(q.contiguous(), kn.contiguous(), vn.contiguous(), variant)
+            strided = run(q, kn, vn, variant)
+        finally:
+            del os.environ["DC_SCAN_VARIANT"]
+        for a, b in zip(dense, strided):
+            assert torch.equal(a, b), variant
+        assert torch.equal(strided[2], kn) and torch.equal(strided[3], vn)   # appended in place from the slices
+    with pytest.raises(ValueError):
+        eng.decode_attend(q.transpose(1, 2), torch.empty_like(q), topk)      # heads not dense: refused, not misread
+    eng.close()
+
+
 def test_fused_step_edge_cases(oracle_lib):
     """Empty store, store smaller than top-k, no resident rows, no new token."""
     from diffcache_b200 import DiffCacheGPU

@@ -518,14 +518,13 @@ lse_combine_kernel(const float* __restrict__ part_acc, int64_t acc_ps, int64_t a
 template <int DT, int LPR>
 int launch_attend(const AttendArgs& a, int n_prob, cudaStream_t stream) {
     // > 48 KB of dynamic shared memory needs an opt-in per kernel and device (not a stream operation)
-    static bool ready[64] = {};
-    int dev = 0;
-    DC_CUDA_TRY(cudaGetDevice(&dev));
-    if (dev < 0 || dev >= 64 || !ready[dev]) {
+    static PerDeviceOnce once;
+    int rc0 = once.run([](int) {
         DC_CUDA_TRY(cudaFuncSetAttribute(sparse_attend_kernel<DT, LPR>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          static_cast<int>(att_smem_bytes<LPR>())));
-        if (dev >= 0 && dev < 64) ready[dev] = true;
-    }
+        return DC_OK;
+    });
+    if (rc0 != DC_OK) return rc0;
     const int chunks = (a.group + kHeadsPerCta - 1) / kHeadsPerCta;
     dim3 grid(static_cast<unsigned>(a.n_split), static_cast<unsigned>(n_prob), static_cast<unsigned>(chunks));
     sparse_attend_kernel<DT, LPR><<<grid, kAttThreads, att_smem_bytes<LPR>(), stream>>>(a);
@@ -677,20 +676,23 @@ constexpr size_t kNoAllocScratchBytes = DC_NOALLOC_SCRATCH_BYTES;
 static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
 
 // Device address of g_noalloc_scratch on the current device (nullptr + error code on failure).
+// The look-up runs once per device under a lock, so first calls from several host threads are safe.
 int noalloc_scratch_ptr(void** out) {
-    static void* ptrs[64] = {};
-    static bool ready[64] = {};
+    static void* ptrs[PerDeviceOnce::kMaxDevices] = {};
+    static PerDeviceOnce once;
     *out = nullptr;
     int dev = 0;
     DC_CUDA_TRY(cudaGetDevice(&dev));
-    DC_REQUIRE(dev >= 0 && dev < 64, "dc_sparse_attend_noalloc: device ordinal %d not supported", dev);
-    if (!ready[dev]) {
+    DC_REQUIRE(dev >= 0 && dev < PerDeviceOnce::kMaxDevices, "dc_sparse_attend_noalloc: device ordinal %d not supported",
+               dev);
+    int rc = once.run([](int d) {
         void* p = nullptr;
         DC_CUDA_TRY(cudaGetSymbolAddress(&p, g_noalloc_scratch));
         DC_REQUIRE(p != nullptr, "dc_sparse_attend_noalloc: no device address for the static scratch array");
-        ptrs[dev] = p;
-        ready[dev] = true;
-    }
+        ptrs[d] = p;
+        return DC_OK;
+    });
+    if (rc != DC_OK) return rc;
     *out = ptrs[dev];
     return DC_OK;
 }

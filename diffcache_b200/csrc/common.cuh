@@ -6,8 +6,10 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
 #include <cstdarg>
 #include <cstdio>
+#include <mutex>
 
 #include "../../include/diffcache_b200.h"
 
@@ -34,6 +36,29 @@ int cuda_fail(cudaError_t err, const char* what);
 inline cudaStream_t as_stream(uint64_t s) { return reinterpret_cast<cudaStream_t>(s); }
 
 int sm_count();  // SMs of the current device (cached per device)
+
+// Runs a set-up step once per CUDA device (kernel attribute opt-ins, symbol address look-ups): the
+// first caller on a device does the work under a lock, later callers only read an atomic flag, so
+// first calls from several host threads do not race.  A step that fails is tried again next time.
+struct PerDeviceOnce {
+    static constexpr int kMaxDevices = 64;
+    std::mutex mu;
+    std::atomic<bool> done[kMaxDevices];
+    PerDeviceOnce() { for (auto& d : done) d.store(false, std::memory_order_relaxed); }
+    template <class F>
+    int run(F&& step) {
+        int dev = 0;
+        cudaError_t err = cudaGetDevice(&dev);
+        if (err != cudaSuccess) return cuda_fail(err, "cudaGetDevice");
+        const bool tracked = dev >= 0 && dev < kMaxDevices;
+        if (tracked && done[dev].load(std::memory_order_acquire)) return DC_OK;
+        std::lock_guard<std::mutex> lock(mu);
+        if (tracked && done[dev].load(std::memory_order_relaxed)) return DC_OK;
+        const int rc = step(dev);
+        if (rc == DC_OK && tracked) done[dev].store(true, std::memory_order_release);
+        return rc;
+    }
+};
 
 // ---- element-type helpers -------------------------------------------------------------------
 // Unpack eight 16-bit elements held in a uint4 into fp32.

@@ -62,13 +62,16 @@ int cuda_fail(cudaError_t err, const char* what) {
 }
 
 int sm_count() {
-    static int cached[64] = {};
+    static std::atomic<int> cached[64];  // zero-initialised; a racing first call stores the same value twice
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess) return 148;
-    if (dev >= 0 && dev < 64 && cached[dev] > 0) return cached[dev];
+    if (dev >= 0 && dev < 64) {
+        const int c = cached[dev].load(std::memory_order_relaxed);
+        if (c > 0) return c;
+    }
     int n = 0;
     if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
-    if (dev >= 0 && dev < 64) cached[dev] = n;
+    if (dev >= 0 && dev < 64) cached[dev].store(n, std::memory_order_relaxed);
     return n;
 }
 

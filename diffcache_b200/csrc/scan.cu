@@ -355,16 +355,15 @@ int launch_scan(const void* keys, int64_t prob_stride, int n_prob, int64_t n, co
     const bool want_tma = variant != nullptr && std::strcmp(variant, "tma") == 0;
     const bool want_narrow = variant != nullptr && std::strcmp(variant, "narrow") == 0;
     if (want_tma) {
-        static bool ready[64] = {};
-        int dev = 0;
-        DC_CUDA_TRY(cudaGetDevice(&dev));
         constexpr int kRing = kTmaStages * kTmaStageBytes;
         constexpr int kQTableMax = 64 * 1024;   // ring + table stay below the 227 KB a CTA may use
-        if (dev < 0 || dev >= 64 || !ready[dev]) {
+        static PerDeviceOnce once;
+        int rc0 = once.run([](int) {
             DC_CUDA_TRY(cudaFuncSetAttribute(score_scan_tma_kernel<DT, LPR>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              kRing + kQTableMax));
-            if (dev >= 0 && dev < 64) ready[dev] = true;
-        }
+            return DC_OK;
+        });
+        if (rc0 != DC_OK) return rc0;
         const size_t table_bytes = static_cast<size_t>(n_prob) * (LPR * 16 + 8);   // queries + (min, max) pairs
         const int q_table = table_bytes <= static_cast<size_t>(kQTableMax) ? 1 : 0;
         score_scan_tma_kernel<DT, LPR><<<sm_count(), kTmaThreads, kRing + (q_table ? table_bytes : 0), stream>>>(

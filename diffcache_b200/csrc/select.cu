@@ -262,15 +262,21 @@ topk_select_kernel(const uint32_t* __restrict__ bits, const uint32_t* __restrict
                 const int sh = shift0 - 32;
                 for (int b = tid; b < kBins; b += kSelThreads) s_hist[b] = 0;
                 __syncthreads();
+                // A caller-supplied (min, max) pair may be narrower than the data: scores outside it are left
+                // out of the sample (they can only mislead it; the exact pass below decides), so that no bin
+                // index ever leaves the histogram.
+                auto sample_one = [&](uint32_t b) {
+                    const uint32_t d = b - lo32;
+                    if (d <= span) atomicAdd(&s_hist[min(d >> sh, static_cast<uint32_t>(kBins - 1))], 1u);
+                };
                 if ((reinterpret_cast<uintptr_t>(p0) & 15) == 0) {
                     const uint4* pv = reinterpret_cast<const uint4*>(p0);
                     for (uint32_t v = tid * 8u; v < (n0 >> 2); v += kSelThreads * 8u) {
                         const uint4 w = pv[v];
-                        atomicAdd(&s_hist[(w.x - lo32) >> sh], 1u); atomicAdd(&s_hist[(w.y - lo32) >> sh], 1u);
-                        atomicAdd(&s_hist[(w.z - lo32) >> sh], 1u); atomicAdd(&s_hist[(w.w - lo32) >> sh], 1u);
+                        sample_one(w.x); sample_one(w.y); sample_one(w.z); sample_one(w.w);
                     }
                 } else {
-                    for (uint32_t i = tid * 8u; i < n0; i += kSelThreads * 8u) atomicAdd(&s_hist[(p0[i] - lo32) >> sh], 1u);
+                    for (uint32_t i = tid * 8u; i < n0; i += kSelThreads * 8u) sample_one(p0[i]);
                 }
                 __syncthreads();
                 {   // U = first bin where the sample count reaches k/8 plus four standard deviations
@@ -452,7 +458,8 @@ topk_select_kernel(const uint32_t* __restrict__ bits, const uint32_t* __restrict
             if (key < lo) {
                 uint32_t pos;
                 if (bucket) {
-                    const uint32_t j = (b - bin_lo32) >> bin_sh;
+                    // (clamped: a caller-supplied key range narrower than the data must not index outside the bins)
+                    const uint32_t j = min((b - bin_lo32) >> bin_sh, static_cast<uint32_t>(kBins - 1));
                     pos = l_cum[j] + atomicAdd(&l_hist[j], 1u);
                 } else {
                     pos = warp_aggregated_inc(&l_ctl->out_count);
@@ -513,11 +520,13 @@ topk_select_kernel(const uint32_t* __restrict__ bits, const uint32_t* __restrict
             if (!bad && p < k_eff) {
                 key = s_out[p];
                 if (static_cast<uint32_t>(p) < base_out) {
-                    const uint32_t j = (static_cast<uint32_t>(key >> 32) - bin_lo32) >> bin_sh;
-                    const uint32_t seg = s_cum[j], cnt = s_hist[j];
+                    const uint32_t j = min((static_cast<uint32_t>(key >> 32) - bin_lo32) >> bin_sh,
+                                           static_cast<uint32_t>(kBins - 1));
+                    const uint32_t seg = s_cum[j];
+                    const uint32_t cnt = min(s_hist[j], static_cast<uint32_t>(k_eff) - min(seg, static_cast<uint32_t>(k_eff)));
                     uint32_t rank = 0;
                     for (uint32_t i = 0; i < cnt; i++) rank += (s_out[seg + i] < key) ? 1u : 0u;
-                    target = static_cast<int>(seg + rank);
+                    target = static_cast<int>(min(seg + rank, static_cast<uint32_t>(k_eff - 1)));
                 }
             }
             const bool live = (!bad && p < k_eff);
@@ -612,13 +621,12 @@ int merge_sorted_count(const uint32_t* bits_all, int world, int n_prob, int k, i
     DC_REQUIRE(smem <= 200 * 1024, "merge_sorted_count: world*k=%lld keys do not fit the 200 KB of shared memory",
                static_cast<long long>(world) * k);
     if (n_prob == 0) return DC_OK;
-    static bool done[64] = {};
-    int dev = 0;
-    DC_CUDA_TRY(cudaGetDevice(&dev));
-    if (dev < 0 || dev >= 64 || !done[dev]) {
+    static PerDeviceOnce once;
+    int rc0 = once.run([](int) {
         DC_CUDA_TRY(cudaFuncSetAttribute(merge_sorted_count_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-        if (dev >= 0 && dev < 64) done[dev] = true;
-    }
+        return DC_OK;
+    });
+    if (rc0 != DC_OK) return rc0;
     merge_sorted_count_kernel<<<n_prob, kMergeThreads, smem, stream>>>(bits_all, world, n_prob, k, my_rank, out_count);
     DC_CUDA_TRY(cudaGetLastError());
     return DC_OK;
@@ -629,14 +637,12 @@ int64_t select_scratch_bytes(int n_prob) { (void)n_prob; return 256; }
 // Opt in to > 48 KB of dynamic shared memory on the current device (not a stream operation;
 // done once per device, outside any graph capture).
 int select_prepare() {
-    static bool done[64] = {};
-    int dev = 0;
-    DC_CUDA_TRY(cudaGetDevice(&dev));
-    if (dev >= 0 && dev < 64 && done[dev]) return DC_OK;
-    DC_CUDA_TRY(cudaFuncSetAttribute(topk_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-    DC_CUDA_TRY(cudaFuncSetAttribute(topk_select_kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 0));
-    if (dev >= 0 && dev < 64) done[dev] = true;
-    return DC_OK;
+    static PerDeviceOnce once;
+    return once.run([](int) {
+        DC_CUDA_TRY(cudaFuncSetAttribute(topk_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        DC_CUDA_TRY(cudaFuncSetAttribute(topk_select_kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 0));
+        return DC_OK;
+    });
 }
 
 // minmax_reset (may be NULL, may alias minmax): per-problem (min, max) pairs that the kernel sets back

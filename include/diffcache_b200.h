@@ -308,11 +308,14 @@ int64_t dc_attend_scratch_bytes(int n_prob, int group, int head_dim);
  * without `scratch`.  Problems whose partials do not fit are rejected with
  * DC_EINVAL and a message naming both sizes (the need is
  * n_prob * splits * group * (head_dim + 2) * 4 bytes, with splits chosen so that
- * n_prob * splits is about four CTAs per SM).  The first call on a device looks
- * the array's device address up and should therefore come before any stream
- * capture.  All calls on a device share the array: calls whose kernels overlap
- * on the GPU race and must be serialised by the caller; stale contents from an
- * earlier call are harmless (every slot is written before it is read).
+ * n_prob * splits is about two CTAs per SM, the same rule dc_sparse_attend uses;
+ * the environment variable DC_ATTEND_CTAS_PER_SM can raise that to at most four).
+ * The first call on a device looks the array's device address up (once, under
+ * a lock, so concurrent first calls are safe) and should therefore come before
+ * any stream capture.  All calls on a device share the array: calls whose
+ * kernels overlap on the GPU race and must be serialised by the caller; stale
+ * contents from an earlier call are harmless (every slot is written before it
+ * is read).
  */
 #define DC_NOALLOC_SCRATCH_BYTES (4 * 1024 * 1024)
 int dc_sparse_attend_noalloc(const void* k_store, const void* v_store, int64_t prob_stride, int64_t n_rows,

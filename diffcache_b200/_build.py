@@ -9,8 +9,9 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(_HERE, "csrc")
 LIB_DIR = os.path.join(_HERE, "_lib")
 LIB_PATH = os.path.join(LIB_DIR, "libdiffcache_b200.so")
-SOURCES = ["scan.cu", "select.cu", "attend.cu", "pq.cu", "budget.cu", "engine.cu"]
-HEADERS = [os.path.join(CSRC, "common.cuh"), os.path.join(_HERE, "..", "include", "diffcache_b200.h")]
+SOURCES = ["scan.cu", "select.cu", "attend.cu", "pq.cu", "budget.cu", "exchange.cu", "engine.cu"]
+HEADERS = [os.path.join(CSRC, "common.cuh"), os.path.join(CSRC, "exchange.cuh"),
+           os.path.join(_HERE, "..", "include", "diffcache_b200.h")]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

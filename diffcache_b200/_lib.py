@@ -29,14 +29,37 @@ SIGNATURES = {
     "dc_decode_attend": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i32, _i32, _f32, _vp, _vp, _vp, _u64]),
     "dc_decode_attend_strided": (_i32, [_vp, _vp, _i64, _vp, _vp, _i64, _vp, _vp, _i64, _i64, _i32, _i32, _f32, _vp, _vp,
                                         _vp, _u64]),
+    "dc_window_push": (_i32, [_vp, _vp, _vp, _i64, _vp, _vp, _i64, _i64, _vp, _u64]),
+    "dc_window_advance": (_i32, [_vp, _u64]),
+    "dc_decode_attend_dyn": (_i32, [_vp, _vp, _i64, _vp, _vp, _i64, _i64, _vp, _i32, _i32, _f32, _vp, _vp, _vp, _u64]),
     "dc_set_adaptive_budget": (_i32, [_vp, _vp, _i32, _f32]),
     "dc_get_budget": (_i32, [_vp, _vp, _u64]),
     "dc_adaptive_budget": (_i32, [_vp, _i64, _i32, _i32, _i32, _vp, _i32, _f32, _vp, _u64]),
     "dc_set_phase_timing": (_i32, [_vp, _i32]),
     "dc_get_phase_times": (_i32, [_vp, ctypes.POINTER(_f32), ctypes.POINTER(_f32), ctypes.POINTER(_f32),
                                   ctypes.POINTER(_i32)]),
+    "dc_trace_begin": (_i32, [_vp, _i32]),
+    "dc_trace_read": (_i32, [_vp, _vp, ctypes.POINTER(_i32)]),
     "dc_local_topk": (_i32, [_vp, _vp, _i32, _vp, _vp, _u64]),
     "dc_attend_owned": (_i32, [_vp, _vp, _vp, _i32, _vp, _vp, _vp, _vp, _i64, _i64, _i32, _f32, _vp, _vp, _vp, _u64]),
+    "dc_xchg_create": (_i32, [_i32, _i32, _i32, _vp, _i32, ctypes.POINTER(_vp)]),
+    "dc_xchg_destroy": (_i32, [_vp]),
+    "dc_xchg_handle_bytes": (_i32, []),
+    "dc_xchg_get_handle": (_i32, [_vp, _vp]),
+    "dc_xchg_open_peer": (_i32, [_vp, _i32, _vp]),
+    "dc_xchg_set_peer": (_i32, [_vp, _i32, _vp]),
+    "dc_xchg_local": (_vp, [_vp]),
+    "dc_xchg_channel": (_vp, [_vp, _i32]),
+    "dc_xchg_set_timeout_ms": (_i32, [_vp, _i32]),
+    "dc_xchg_push": (_i32, [_vp, _i32, _vp, _i64, _u64]),
+    "dc_xchg_push_rows": (_i32, [_vp, _i32, _vp, _i64, _i64, _u64]),
+    "dc_xchg_wait": (_i32, [_vp, _i32, _u64]),
+    "dc_xchg_check": (_i32, [_vp, _u64]),
+    "dc_sharded_slot_bytes": (_i32, [_vp, _i32, _vp]),
+    "dc_sharded_local": (_i32, [_vp, _vp, _vp, _i32, _u64]),
+    "dc_sharded_attend": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i32, _f32, _u64]),
+    "dc_sharded_combine": (_i32, [_vp, _vp, _vp, _vp, _u64]),
+    "dc_sharded_decode_attend": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i32, _i32, _f32, _vp, _vp, _u64]),
     "dc_merge_sorted_count": (_i32, [_vp, _i32, _i32, _i32, _i32, _vp, _u64]),
     "dc_score_scan": (_i32, [_vp, _i64, _i32, _i64, _i32, _i32, _vp, _i32, _i32, _vp, _i64, _vp, _u64]),
     "dc_select_scratch_bytes": (_i64, [_i32]),

@@ -12,7 +12,7 @@
 #include <cmath>
 #include <cstdlib>
 
-#include "common.cuh"
+#include "exchange.cuh"
 
 namespace dc {
 
@@ -43,6 +43,8 @@ struct AttendArgs {
     uint16_t* res_v;
     int64_t res_stride_b, res_stride_h;
     int res_len;
+    const int32_t* n_rows_dev;   // optional device words overriding n_rows / res_len when the kernel runs
+    const int32_t* res_len_dev;  // (launches replayed from a graph while the lengths change)
     float scale_log2;      // softmax scale * log2(e)
     int n_split;
     float* part_acc;       // (n_prob, group, n_split, D)
@@ -136,6 +138,10 @@ __device__ __forceinline__ int swz(int row, int chunk) { return row * (D * 2) + 
 template <int DT, int LPR>
 __global__ void __launch_bounds__(kAttThreads)
 sparse_attend_kernel(const AttendArgs a) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int64_t n_rows = a.n_rows_dev != nullptr ? static_cast<int64_t>(*a.n_rows_dev) : a.n_rows;
+    const int res_len = a.res_len_dev != nullptr ? *a.res_len_dev : a.res_len;
     constexpr int D = LPR * 8;
     constexpr int RB = AttCfg<LPR>::RB;
     constexpr int NS = AttCfg<LPR>::NS;
@@ -163,7 +169,7 @@ sparse_attend_kernel(const AttendArgs a) {
 
     const int has_new = a.k_new != nullptr ? 1 : 0;
     const int64_t new_off = a.new_stride_b ? b * a.new_stride_b + static_cast<int64_t>(h) * D : prob * D;
-    const int total = a.n_sel + a.res_len + has_new;
+    const int total = a.n_sel + res_len + has_new;
     const int per = (total + a.n_split - 1) / a.n_split;
     const int j0 = min(total, split * per);
     const int j1 = min(total, j0 + per);
@@ -190,9 +196,9 @@ sparse_attend_kernel(const AttendArgs a) {
 
     // flash-attn's in-place append of the new token (base.py:134-142): one CTA per problem
     if (has_new && split == 0 && blockIdx.z == 0 && rk != nullptr && tid < LPR) {
-        reinterpret_cast<uint4*>(rk + static_cast<int64_t>(a.res_len) * D)[tid] =
+        reinterpret_cast<uint4*>(rk + static_cast<int64_t>(res_len) * D)[tid] =
             reinterpret_cast<const uint4*>(a.k_new + new_off)[tid];
-        reinterpret_cast<uint4*>(rv + static_cast<int64_t>(a.res_len) * D)[tid] =
+        reinterpret_cast<uint4*>(rv + static_cast<int64_t>(res_len) * D)[tid] =
             reinterpret_cast<const uint4*>(a.v_new + new_off)[tid];
     }
 
@@ -221,13 +227,13 @@ sparse_attend_kernel(const AttendArgs a) {
                 for (int i = 0; i < NCOPY; i++) {
                     const uint32_t id = __shfl_sync(0xFFFFFFFFu, my_id, sub * LPR + i);
                     const int64_t row = static_cast<int64_t>(id) - a.sel_base;
-                    const bool ok = row >= 0 && row < a.n_rows;  // ids of other shards and pads are skipped
+                    const bool ok = row >= 0 && row < n_rows;  // ids of other shards and pads are skipped
                     const uint16_t* kp = ok ? kst_col + row * D : a.q;
                     cp_async16(ks + soff[i], kp, ok ? 16 : 0);
                     cp_async16(vs + soff[i], ok ? kp + v_minus_k : a.q, ok ? 16 : 0);
                     if (col == 0) s_valid[t % NS][warp * RW + i * R + sub] = ok ? 1 : 0;
                 }
-            } else if (jt >= a.n_sel && jt + TILE <= min(j1, a.n_sel + a.res_len)) {
+            } else if (jt >= a.n_sel && jt + TILE <= min(j1, a.n_sel + res_len)) {
                 // a tile of resident (sink / window) rows: consecutive rows of the caller's buffer
                 const uint16_t* kp0 = rk + static_cast<int64_t>(jt - a.n_sel + warp * RW + sub) * D + col * 8;
                 const int64_t rv_minus_rk = rv - rk;
@@ -249,8 +255,8 @@ sparse_attend_kernel(const AttendArgs a) {
                     if (j < j1) {
                         if (j < a.n_sel) {
                             const int64_t row = static_cast<int64_t>(id) - a.sel_base;
-                            if (row >= 0 && row < a.n_rows) { kp = kst + row * D; vp = vst + row * D; }
-                        } else if (j < a.n_sel + a.res_len) {
+                            if (row >= 0 && row < n_rows) { kp = kst + row * D; vp = vst + row * D; }
+                        } else if (j < a.n_sel + res_len) {
                             const int64_t row = j - a.n_sel;
                             kp = rk + row * D; vp = rv + row * D;
                         } else {
@@ -429,7 +435,10 @@ __global__ void __launch_bounds__(kCombineThreads)
 lse_combine_kernel(const float* __restrict__ part_acc, int64_t acc_ps, int64_t acc_rs,
                    const float* __restrict__ part_ml, int64_t ml_ps, int64_t ml_rs, int n_part, int dim,
                    uint16_t* __restrict__ out, float* __restrict__ out_lse, float* __restrict__ out_acc,
-                   float* __restrict__ out_ml) {
+                   float* __restrict__ out_ml, const XchgWait wait) {
+    pdl_launch_dependents();
+    pdl_wait();
+    xchg_wait_all(wait);   // parts delivered by peer stores: wait until every rank's has arrived (no-op otherwise)
     const int64_t row = blockIdx.x;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     __shared__ float s_w[kCombineMaxParts];   // weight of every part: exp2(m_s - M)
@@ -527,8 +536,7 @@ int launch_attend(const AttendArgs& a, int n_prob, cudaStream_t stream) {
     if (rc0 != DC_OK) return rc0;
     const int chunks = (a.group + kHeadsPerCta - 1) / kHeadsPerCta;
     dim3 grid(static_cast<unsigned>(a.n_split), static_cast<unsigned>(n_prob), static_cast<unsigned>(chunks));
-    sparse_attend_kernel<DT, LPR><<<grid, kAttThreads, att_smem_bytes<LPR>(), stream>>>(a);
-    DC_CUDA_TRY(cudaGetLastError());
+    DC_CUDA_TRY(launch_chained(sparse_attend_kernel<DT, LPR>, grid, dim3(kAttThreads), att_smem_bytes<LPR>(), stream, 0u, a));
     return DC_OK;
 }
 
@@ -555,21 +563,20 @@ int64_t attend_scratch_bytes(int n_prob, int group, int head_dim) {
 
 int lse_combine(const float* acc, int64_t acc_ps, int64_t acc_rs, const float* ml, int64_t ml_ps, int64_t ml_rs,
                 int n_part, int64_t rows, int head_dim, int dtype, void* out, float* out_lse, float* out_acc,
-                float* out_ml, cudaStream_t stream) {
+                float* out_ml, cudaStream_t stream, const XchgWait* wait) {
     DC_REQUIRE(acc && ml && n_part >= 1 && rows >= 0, "lse_combine: bad arguments");
     DC_REQUIRE(dtype == DC_BF16 || dtype == DC_FP16, "lse_combine: dtype %d not supported", dtype);
     DC_REQUIRE(n_part <= kCombineMaxParts, "lse_combine: n_part=%d exceeds %d", n_part, kCombineMaxParts);
     if (rows == 0) return DC_OK;
-    const int threads = kCombineThreads;
+    const dim3 grid(static_cast<unsigned>(rows)), block(kCombineThreads);
+    XchgWait w = {};
+    if (wait != nullptr) w = *wait;
     if (dtype == DC_BF16)
-        lse_combine_kernel<DC_BF16><<<static_cast<unsigned>(rows), threads, 0, stream>>>(
-            acc, acc_ps, acc_rs, ml, ml_ps, ml_rs, n_part, head_dim, static_cast<uint16_t*>(out), out_lse, out_acc,
-            out_ml);
+        DC_CUDA_TRY(launch_chained(lse_combine_kernel<DC_BF16>, grid, block, 0, stream, 0u, acc, acc_ps, acc_rs, ml, ml_ps,
+                                   ml_rs, n_part, head_dim, static_cast<uint16_t*>(out), out_lse, out_acc, out_ml, w));
     else
-        lse_combine_kernel<DC_FP16><<<static_cast<unsigned>(rows), threads, 0, stream>>>(
-            acc, acc_ps, acc_rs, ml, ml_ps, ml_rs, n_part, head_dim, static_cast<uint16_t*>(out), out_lse, out_acc,
-            out_ml);
-    DC_CUDA_TRY(cudaGetLastError());
+        DC_CUDA_TRY(launch_chained(lse_combine_kernel<DC_FP16>, grid, block, 0, stream, 0u, acc, acc_ps, acc_rs, ml, ml_ps,
+                                   ml_rs, n_part, head_dim, static_cast<uint16_t*>(out), out_lse, out_acc, out_ml, w));
     return DC_OK;
 }
 
@@ -578,7 +585,10 @@ int sparse_attend(const void* k_store, const void* v_store, int64_t prob_stride,
                   int64_t sel_stride, int n_sel, int64_t sel_base, const void* k_new, const void* v_new, void* res_k,
                   void* res_v, int64_t res_stride_b, int64_t res_stride_h, int res_len, float scale, void* out,
                   float* out_lse, float* out_acc, float* out_ml, void* scratch, cudaStream_t stream,
-                  const int32_t* sel_count, int64_t q_stride_b, int64_t new_stride_b) {
+                  const int32_t* sel_count, int64_t q_stride_b, int64_t new_stride_b, const int32_t* n_rows_dev,
+                  const int32_t* res_len_dev) {
+    // n_rows_dev / res_len_dev (may be NULL): device words read when the kernel runs, overriding n_rows and
+    // res_len, which then only size the launch (res_len = the most resident rows there can be)
     DC_REQUIRE(q != nullptr && scratch != nullptr, "sparse_attend: null q/scratch");
     DC_REQUIRE(q_stride_b % 8 == 0 && new_stride_b % 8 == 0, "sparse_attend: batch strides must be multiples of 8 elements");
     DC_REQUIRE(dtype == DC_BF16 || dtype == DC_FP16, "sparse_attend: dtype %d not supported", dtype);
@@ -625,6 +635,8 @@ int sparse_attend(const void* k_store, const void* v_store, int64_t prob_stride,
     a.res_stride_b = res_stride_b;
     a.res_stride_h = res_stride_h;
     a.res_len = res_len;
+    a.n_rows_dev = n_rows_dev;
+    a.res_len_dev = res_len_dev;
     a.scale_log2 = (scale > 0.0f ? scale : 1.0f / std::sqrt(static_cast<float>(head_dim))) * kLog2e;
     a.n_split = attend_splits(n_prob, total);
     a.part_acc = static_cast<float*>(scratch);
@@ -645,7 +657,7 @@ int sparse_attend(const void* k_store, const void* v_store, int64_t prob_stride,
     if (rc != DC_OK) return rc;
     return lse_combine(a.part_acc, head_dim, static_cast<int64_t>(a.n_split) * head_dim, a.part_ml, 2,
                        static_cast<int64_t>(a.n_split) * 2, a.n_split, static_cast<int64_t>(n_prob) * group, head_dim,
-                       dtype, out, out_lse, out_acc, out_ml, stream);
+                       dtype, out, out_lse, out_acc, out_ml, stream, nullptr);
 }
 
 }  // namespace dc
@@ -725,5 +737,5 @@ extern "C" int dc_sparse_attend_noalloc(const void* k_store, const void* v_store
     if (rc != DC_OK) return rc;
     return sparse_attend(k_store, v_store, prob_stride, n_rows, n_prob, kv_heads, group, head_dim, dtype, q, sel,
                          sel_stride, n_sel, sel_base, k_new, v_new, res_k, res_v, res_stride_b, res_stride_h, res_len,
-                         scale, out, out_lse, out_acc, out_ml, scratch, as_stream(stream), nullptr, 0, 0);
+                         scale, out, out_lse, out_acc, out_ml, scratch, as_stream(stream), nullptr, 0, 0, nullptr, nullptr);
 }

@@ -37,10 +37,17 @@ __device__ __forceinline__ double block_sum(double v, double* scratch) {
 
 // bits: (n_prob, stride) best-first ranking keys; budget[p] = first passing checkpoint or k.
 __global__ void __launch_bounds__(kBudgetThreads)
-adaptive_budget_kernel(const uint32_t* __restrict__ bits, int64_t stride, int k, float sqrt_dim,
-                       BudgetSeq seq, float threshold, int32_t* __restrict__ budget) {
+adaptive_budget_kernel(const uint32_t* __restrict__ bits, int64_t stride, int k, const int32_t* __restrict__ n_dev,
+                       float sqrt_dim, BudgetSeq seq, float threshold, int32_t* __restrict__ budget) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ double scratch[kBudgetThreads / 32];
     const int64_t prob = blockIdx.x;
+    if (n_dev != nullptr) k = min(k, *n_dev);  // keys beyond the rows the store holds are pads
+    if (k <= 0) {
+        if (threadIdx.x == 0) budget[prob] = 0;
+        return;
+    }
     const uint32_t* b = bits + prob * stride;
     const int tid = threadIdx.x;
     const float z0 = (65536.0f - __uint_as_float(b[0])) / sqrt_dim;  // best logit = maximum of every head
@@ -83,7 +90,7 @@ adaptive_budget_kernel(const uint32_t* __restrict__ bits, int64_t stride, int k,
 }  // namespace
 
 int adaptive_budget(const uint32_t* bits, int64_t stride, int n_prob, int k, int head_dim, const int* seq, int n_seq,
-                    float threshold, int32_t* budget, cudaStream_t stream) {
+                    float threshold, int32_t* budget, cudaStream_t stream, const int32_t* n_dev) {
     DC_REQUIRE(bits && budget, "adaptive_budget: null pointer");
     DC_REQUIRE(n_prob >= 0 && k >= 1 && head_dim >= 1, "adaptive_budget: bad sizes");
     DC_REQUIRE(n_seq >= 0 && n_seq <= kMaxCheckpoints && (n_seq == 0 || seq != nullptr),
@@ -92,9 +99,8 @@ int adaptive_budget(const uint32_t* bits, int64_t stride, int n_prob, int k, int
     BudgetSeq s;
     s.n = n_seq;
     for (int i = 0; i < kMaxCheckpoints; i++) s.h[i] = i < n_seq ? seq[i] : 0;
-    adaptive_budget_kernel<<<n_prob, kBudgetThreads, 0, stream>>>(bits, stride, k, sqrtf(static_cast<float>(head_dim)),
-                                                                  s, threshold, budget);
-    DC_CUDA_TRY(cudaGetLastError());
+    DC_CUDA_TRY(launch_chained(adaptive_budget_kernel, dim3(n_prob), dim3(kBudgetThreads), 0, stream, 0u, bits, stride, k,
+                               n_dev, sqrtf(static_cast<float>(head_dim)), s, threshold, budget));
     return DC_OK;
 }
 

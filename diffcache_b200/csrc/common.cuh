@@ -60,6 +60,47 @@ struct PerDeviceOnce {
     }
 };
 
+// ---- programmatic dependent launch --------------------------------------------------------------
+// The kernels of a decode step run back to back on one stream, each consuming what the one before it
+// wrote.  Launched with cudaLaunchAttributeProgrammaticStreamSerialization, a kernel may be scheduled
+// while its predecessor is still draining: every kernel here first lets ITS successor be scheduled
+// (pdl_launch_dependents), does the set-up that touches no global data, and then blocks in pdl_wait
+// until the predecessor grid has completed and its writes are visible.  Both instructions do nothing
+// in a kernel that was launched the ordinary way.  Every kernel of the chain executes pdl_wait, so
+// "kernel N finished" still implies "kernels 1..N-1 finished".
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+
+bool pdl_enabled();  // false when the environment variable DC_PDL is "0"
+
+// cudaLaunchKernelEx with the programmatic-serialization attribute (and a cluster size when cluster_x > 0).
+template <class... KArgs, class... Args>
+inline cudaError_t launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                  unsigned cluster_x, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    unsigned n_attr = 0;
+    if (pdl_enabled()) {
+        attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
+        n_attr++;
+    }
+    if (cluster_x > 0) {
+        attr[n_attr].id = cudaLaunchAttributeClusterDimension;
+        attr[n_attr].val.clusterDim.x = cluster_x;
+        attr[n_attr].val.clusterDim.y = 1;
+        attr[n_attr].val.clusterDim.z = 1;
+        n_attr++;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = n_attr;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 // ---- element-type helpers -------------------------------------------------------------------
 // Unpack eight 16-bit elements held in a uint4 into fp32.
 template <int DT>

@@ -31,9 +31,13 @@ constexpr int kLoadsPerTile = 8;  // 16-byte loads in flight per lane
 // grid = (chunks, n_prob); each CTA streams `rows_per_cta` consecutive rows of one problem.
 template <int DT, int LPR>
 __global__ void __launch_bounds__(kScanThreads)
-score_scan_kernel(const uint16_t* __restrict__ keys, int64_t prob_stride, int64_t n, const uint16_t* __restrict__ q,
-                  int q_mode, int group, int kv_heads, int64_t q_stride_b, uint32_t* __restrict__ scores,
-                  int64_t score_stride, uint32_t* __restrict__ minmax, int rows_per_cta) {
+score_scan_kernel(const uint16_t* __restrict__ keys, int64_t prob_stride, int64_t n, const int32_t* __restrict__ n_dev,
+                  const uint16_t* __restrict__ q, int q_mode, int group, int kv_heads, int64_t q_stride_b,
+                  uint32_t* __restrict__ scores, int64_t score_stride, uint32_t* __restrict__ minmax, int rows_per_cta) {
+    pdl_launch_dependents();
+    pdl_wait();
+    if (n_dev != nullptr) n = *n_dev;   // rows valid now (the grid was sized for an upper bound)
+    if (static_cast<int64_t>(blockIdx.x) * rows_per_cta >= n) return;
     constexpr int D = LPR * 8;
     constexpr int R = 32 / LPR;               // rows covered by one warp-wide load
     constexpr int TR = kLoadsPerTile * R;     // rows per warp tile
@@ -108,9 +112,14 @@ score_scan_kernel(const uint16_t* __restrict__ keys, int64_t prob_stride, int64_
 // load covers 32/LW consecutive rows = 1 KB.  Half the load instructions per byte.
 template <int DT, int LW>
 __global__ void __launch_bounds__(kScanThreads)
-score_scan_wide_kernel(const uint16_t* __restrict__ keys, int64_t prob_stride, int64_t n, const uint16_t* __restrict__ q,
-                       int q_mode, int group, int kv_heads, int64_t q_stride_b, uint32_t* __restrict__ scores,
-                       int64_t score_stride, uint32_t* __restrict__ minmax, int rows_per_cta) {
+score_scan_wide_kernel(const uint16_t* __restrict__ keys, int64_t prob_stride, int64_t n,
+                       const int32_t* __restrict__ n_dev, const uint16_t* __restrict__ q, int q_mode, int group,
+                       int kv_heads, int64_t q_stride_b, uint32_t* __restrict__ scores, int64_t score_stride,
+                       uint32_t* __restrict__ minmax, int rows_per_cta) {
+    pdl_launch_dependents();
+    pdl_wait();
+    if (n_dev != nullptr) n = *n_dev;   // rows valid now (the grid was sized for an upper bound)
+    if (static_cast<int64_t>(blockIdx.x) * rows_per_cta >= n) return;
     constexpr int D = LW * 16;
     constexpr int R = 32 / LW;
     constexpr int TR = kLoadsPerTile * R;
@@ -205,10 +214,13 @@ __device__ __forceinline__ void mbar_arrive(unsigned long long* bar) {
 // a wait that runs out stores 201 (producer) or 202 (consumer) in *status and the thread leaves.
 template <int DT, int LPR>
 __global__ void __launch_bounds__(kTmaThreads, 1)
-score_scan_tma_kernel(const uint16_t* __restrict__ keys, int64_t prob_stride, int64_t n, int n_prob,
-                      const uint16_t* __restrict__ q, int q_mode, int group, int kv_heads, int64_t q_stride_b,
-                      uint32_t* __restrict__ scores, int64_t score_stride, uint32_t* __restrict__ minmax,
-                      uint32_t* __restrict__ status, int q_table) {
+score_scan_tma_kernel(const uint16_t* __restrict__ keys, int64_t prob_stride, int64_t n,
+                      const int32_t* __restrict__ n_dev, int n_prob, const uint16_t* __restrict__ q, int q_mode,
+                      int group, int kv_heads, int64_t q_stride_b, uint32_t* __restrict__ scores, int64_t score_stride,
+                      uint32_t* __restrict__ minmax, uint32_t* __restrict__ status, int q_table) {
+    pdl_launch_dependents();
+    pdl_wait();
+    if (n_dev != nullptr) n = *n_dev;
     constexpr int D = LPR * 8;
     constexpr int R = 32 / LPR;
     constexpr int TR = kLoadsPerTile * R;
@@ -344,8 +356,9 @@ int env_int(const char* name, int dflt) {
 }
 
 template <int DT, int LPR>
-int launch_scan(const void* keys, int64_t prob_stride, int n_prob, int64_t n, const void* q, int q_mode, int group,
-                int kv_heads, int64_t q_stride_b, uint32_t* scores, int64_t score_stride, uint32_t* minmax, uint32_t* status, cudaStream_t stream) {
+int launch_scan(const void* keys, int64_t prob_stride, int n_prob, int64_t n, const int32_t* n_dev, const void* q,
+                int q_mode, int group, int kv_heads, int64_t q_stride_b, uint32_t* scores, int64_t score_stride,
+                uint32_t* minmax, uint32_t* status, cudaStream_t stream) {
     constexpr int TR = kLoadsPerTile * (32 / LPR);
     static int rows_cfg = env_int("DC_SCAN_ROWS_PER_CTA", 1024);
     int rows_per_cta = ((rows_cfg + kScanWarps * TR - 1) / (kScanWarps * TR)) * (kScanWarps * TR);
@@ -366,32 +379,33 @@ int launch_scan(const void* keys, int64_t prob_stride, int n_prob, int64_t n, co
         if (rc0 != DC_OK) return rc0;
         const size_t table_bytes = static_cast<size_t>(n_prob) * (LPR * 16 + 8);   // queries + (min, max) pairs
         const int q_table = table_bytes <= static_cast<size_t>(kQTableMax) ? 1 : 0;
-        score_scan_tma_kernel<DT, LPR><<<sm_count(), kTmaThreads, kRing + (q_table ? table_bytes : 0), stream>>>(
-            static_cast<const uint16_t*>(keys), prob_stride, n, n_prob, static_cast<const uint16_t*>(q), q_mode, group,
-            kv_heads, q_stride_b, scores, score_stride, minmax, status, q_table);
-        DC_CUDA_TRY(cudaGetLastError());
+        DC_CUDA_TRY(launch_chained(score_scan_tma_kernel<DT, LPR>, dim3(sm_count()), dim3(kTmaThreads),
+                                   kRing + (q_table ? table_bytes : 0), stream, 0u, static_cast<const uint16_t*>(keys),
+                                   prob_stride, n, n_dev, n_prob, static_cast<const uint16_t*>(q), q_mode, group, kv_heads,
+                                   q_stride_b, scores, score_stride, minmax, status, q_table));
         return DC_OK;
     }
     if (!want_narrow && LPR >= 8 && prob_stride % 16 == 0 && (reinterpret_cast<uintptr_t>(keys) & 31) == 0) {
         // rows_per_cta is a multiple of 8 warps x 8 loads x (32 / (LPR/2)) rows as well (LPR >= 8)
-        score_scan_wide_kernel<DT, LPR / 2><<<grid, kScanThreads, 0, stream>>>(
-            static_cast<const uint16_t*>(keys), prob_stride, n, static_cast<const uint16_t*>(q), q_mode, group, kv_heads,
-            q_stride_b, scores, score_stride, minmax, rows_per_cta);
-        DC_CUDA_TRY(cudaGetLastError());
+        DC_CUDA_TRY(launch_chained(score_scan_wide_kernel<DT, LPR / 2>, grid, dim3(kScanThreads), 0, stream, 0u,
+                                   static_cast<const uint16_t*>(keys), prob_stride, n, n_dev,
+                                   static_cast<const uint16_t*>(q), q_mode, group, kv_heads, q_stride_b, scores,
+                                   score_stride, minmax, rows_per_cta));
         return DC_OK;
     }
-    score_scan_kernel<DT, LPR><<<grid, kScanThreads, 0, stream>>>(
-        static_cast<const uint16_t*>(keys), prob_stride, n, static_cast<const uint16_t*>(q), q_mode, group, kv_heads,
-        q_stride_b, scores, score_stride, minmax, rows_per_cta);
-    DC_CUDA_TRY(cudaGetLastError());
+    DC_CUDA_TRY(launch_chained(score_scan_kernel<DT, LPR>, grid, dim3(kScanThreads), 0, stream, 0u,
+                               static_cast<const uint16_t*>(keys), prob_stride, n, n_dev, static_cast<const uint16_t*>(q),
+                               q_mode, group, kv_heads, q_stride_b, scores, score_stride, minmax, rows_per_cta));
     return DC_OK;
 }
 
 }  // namespace
 
+// n: rows per problem the launch is sized for; n_dev (may be NULL): device word holding the number of rows
+// that are valid when the kernel runs (<= n), for launches replayed from a graph while the store grows.
 int score_scan(const void* keys, int64_t prob_stride, int n_prob, int64_t n, int head_dim, int dtype, const void* q,
                int q_mode, int group, uint32_t* scores, int64_t score_stride, uint32_t* minmax, cudaStream_t stream,
-               uint32_t* status, int kv_heads, int64_t q_stride_b) {
+               uint32_t* status, int kv_heads, int64_t q_stride_b, const int32_t* n_dev) {
     DC_REQUIRE(keys && q && scores, "score_scan: null pointer");
     DC_REQUIRE(dtype == DC_BF16 || dtype == DC_FP16, "score_scan: dtype %d not supported", dtype);
     DC_REQUIRE(head_dim == 64 || head_dim == 128 || head_dim == 256, "score_scan: head_dim %d not in {64,128,256}",
@@ -407,7 +421,7 @@ int score_scan(const void* keys, int64_t prob_stride, int n_prob, int64_t n, int
                "score_scan: keys/q must be 16-byte aligned and prob_stride a multiple of 8 elements");
     if (n_prob == 0 || n == 0) return DC_OK;
 #define DC_SCAN_CASE(DT, LPR) \
-    return launch_scan<DT, LPR>(keys, prob_stride, n_prob, n, q, q_mode, group, kv_heads, q_stride_b, scores, \
+    return launch_scan<DT, LPR>(keys, prob_stride, n_prob, n, n_dev, q, q_mode, group, kv_heads, q_stride_b, scores, \
                                 score_stride, minmax, status, stream)
     if (dtype == DC_BF16) {
         if (head_dim == 64) DC_SCAN_CASE(DC_BF16, 8);

@@ -18,7 +18,7 @@
 
 #include <algorithm>
 
-#include "common.cuh"
+#include "exchange.cuh"
 
 namespace cg = cooperative_groups;
 
@@ -133,9 +133,12 @@ __device__ __forceinline__ void for_each_score(const uint32_t* __restrict__ pb, 
 // dynamic shared memory: out[kpad] u64 | cand[kCandCap] u64 | hist[kBins] u32 | cum[kBins] u32 | raw[raw_cap] u64
 __global__ void __launch_bounds__(kSelThreads, 1)
 topk_select_kernel(const uint32_t* __restrict__ bits, const uint32_t* __restrict__ ids, int64_t in_stride, int64_t n,
-                   int k, const uint32_t* minmax, uint32_t* minmax_reset, uint32_t id_offset,
-                   uint32_t* __restrict__ out_bits, uint32_t* __restrict__ out_ids, int64_t out_stride, int kpad,
-                   int raw_cap, uint32_t* __restrict__ status) {
+                   const int32_t* __restrict__ n_dev, int k, const uint32_t* minmax, uint32_t* minmax_reset,
+                   uint32_t id_offset, uint32_t* __restrict__ out_bits, uint32_t* __restrict__ out_ids,
+                   int64_t out_stride, int kpad, int raw_cap, uint32_t* __restrict__ status) {
+    pdl_launch_dependents();
+    pdl_wait();
+    if (n_dev != nullptr) n = min(n, static_cast<int64_t>(*n_dev));  // scores valid now (n is the launch's upper bound)
     cg::cluster_group cluster = cg::this_cluster();
     const unsigned rank = cluster.block_rank();
     const unsigned csize = cluster.num_blocks();
@@ -563,13 +566,16 @@ int pow2_floor(int x) { int p = 1; while (p * 2 <= x) p *= 2; return p; }
 constexpr int kMergeThreads = 1024;
 
 __global__ void __launch_bounds__(kMergeThreads)
-merge_sorted_count_kernel(const uint32_t* __restrict__ bits_all, int world, int n_prob, int k, int my_rank,
-                          int32_t* __restrict__ out_count) {
+merge_sorted_count_kernel(const uint32_t* __restrict__ bits_all, int64_t rank_stride, int world, int n_prob, int k,
+                          int my_rank, int32_t* __restrict__ out_count, const XchgWait wait) {
+    pdl_launch_dependents();
+    pdl_wait();
+    xchg_wait_all(wait);   // lists delivered by peer stores: wait until every rank's has arrived (no-op otherwise)
     extern __shared__ __align__(16) uint32_t s_lists[];
     __shared__ int s_sum[kMergeThreads / 32];
     const int p = blockIdx.x, tid = threadIdx.x;
     for (int r = 0; r < world; r++) {
-        const uint32_t* src = bits_all + (static_cast<int64_t>(r) * n_prob + p) * k;
+        const uint32_t* src = bits_all + r * rank_stride + static_cast<int64_t>(p) * k;   // rank r's (n_prob, k) lists
         uint32_t* dst = s_lists + static_cast<size_t>(r) * k;
         if ((k & 3) == 0 && (reinterpret_cast<uintptr_t>(src) & 15) == 0) {
             for (int i = tid; i < k / 4; i += kMergeThreads)
@@ -611,8 +617,10 @@ merge_sorted_count_kernel(const uint32_t* __restrict__ bits_all, int world, int 
 
 }  // namespace
 
+// rank_stride: elements between two ranks' (n_prob, k) lists; 0 = dense (n_prob * k).
 int merge_sorted_count(const uint32_t* bits_all, int world, int n_prob, int k, int my_rank, int32_t* out_count,
-                       cudaStream_t stream) {
+                       cudaStream_t stream, const XchgWait* wait, int64_t rank_stride) {
+    if (rank_stride == 0) rank_stride = static_cast<int64_t>(n_prob) * k;
     DC_REQUIRE(bits_all && out_count, "merge_sorted_count: null pointer");
     DC_REQUIRE(world >= 1 && my_rank >= 0 && my_rank < world, "merge_sorted_count: rank %d of %d", my_rank, world);
     DC_REQUIRE(k >= 1 && k <= DC_MAX_TOPK, "merge_sorted_count: k=%d outside [1, %d]", k, DC_MAX_TOPK);
@@ -627,8 +635,10 @@ int merge_sorted_count(const uint32_t* bits_all, int world, int n_prob, int k, i
         return DC_OK;
     });
     if (rc0 != DC_OK) return rc0;
-    merge_sorted_count_kernel<<<n_prob, kMergeThreads, smem, stream>>>(bits_all, world, n_prob, k, my_rank, out_count);
-    DC_CUDA_TRY(cudaGetLastError());
+    XchgWait w = {};
+    if (wait != nullptr) w = *wait;
+    DC_CUDA_TRY(launch_chained(merge_sorted_count_kernel, dim3(n_prob), dim3(kMergeThreads), smem, stream, 0u, bits_all,
+                               rank_stride, world, n_prob, k, my_rank, out_count, w));
     return DC_OK;
 }
 
@@ -647,9 +657,11 @@ int select_prepare() {
 
 // minmax_reset (may be NULL, may alias minmax): per-problem (min, max) pairs that the kernel sets back
 // to (0xFFFFFFFF, 0) once it has read them, ready for the next scan's atomic min / max.
+// n: scores per problem the launch is sized for; n_dev (may be NULL): device word with the number that is
+// valid when the kernel runs (<= n).
 int topk_select(const uint32_t* bits, const uint32_t* ids, int64_t in_stride, int n_prob, int64_t n, int k,
                 const uint32_t* minmax, uint32_t id_offset, uint32_t* out_bits, uint32_t* out_ids, int64_t out_stride,
-                uint32_t* status, cudaStream_t stream, uint32_t* minmax_reset) {
+                uint32_t* status, cudaStream_t stream, uint32_t* minmax_reset, const int32_t* n_dev) {
     DC_REQUIRE(bits != nullptr, "topk_select: null scores");
     DC_REQUIRE(k >= 0 && k <= DC_MAX_TOPK, "topk_select: k=%d outside [0, %d]", k, DC_MAX_TOPK);
     DC_REQUIRE(n >= 0 && n < (1ll << 32), "topk_select: n=%lld outside [0, 2^32)", static_cast<long long>(n));
@@ -671,20 +683,10 @@ int topk_select(const uint32_t* bits, const uint32_t* ids, int64_t in_stride, in
     while (by_work < 8 && static_cast<int64_t>(by_work) * 16384 < n) by_work <<= 1;
     csize = std::min(csize, by_work);
 
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(static_cast<unsigned>(csize), static_cast<unsigned>(n_prob), 1);
-    cfg.blockDim = dim3(kSelThreads, 1, 1);
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = static_cast<unsigned>(csize);
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    DC_CUDA_TRY(cudaLaunchKernelEx(&cfg, topk_select_kernel, bits, ids, in_stride, n, k, minmax, minmax_reset, id_offset,
-                                   out_bits, out_ids, out_stride, kpad, raw_cap, status));
+    DC_CUDA_TRY(launch_chained(topk_select_kernel, dim3(static_cast<unsigned>(csize), static_cast<unsigned>(n_prob), 1),
+                               dim3(kSelThreads, 1, 1), smem, stream, static_cast<unsigned>(csize), bits, ids, in_stride, n,
+                               n_dev, k, minmax, minmax_reset, id_offset, out_bits, out_ids, out_stride, kpad, raw_cap,
+                               status));
     return DC_OK;
 }
 

@@ -9,6 +9,7 @@ a numpy array (host) or a torch tensor (host or CUDA).
 from __future__ import annotations
 
 import ctypes
+import time
 from typing import Optional, Sequence
 
 import numpy as np
@@ -34,9 +35,18 @@ def init_metrics() -> None:
     """Counterpart of ``diffcache._cpu.init_metrics`` (lib.rs:662-665).
 
     The reference installs a TCP exporter for its per-layer latency counters; this
-    engine keeps its counters in ``DiffCacheGPU.metrics`` instead, so there is
-    nothing to install."""
+    engine keeps the same counters, under the reference's names, in
+    ``DiffCacheGPU.metrics`` instead, so there is nothing to install."""
     return None
+
+
+def _metric_names(name: str) -> dict:
+    """The reference's counters (microseconds for the latencies): ``{name}_num_searches`` and
+    ``{name}_search_latency`` per (batch, kv-head) search (nsw.rs:595,618), ``{name}_collect_latency``
+    (nsw.rs:660), ``{name}_total_query_latency`` per query call (lib.rs:403); ``{name}_num_queries``
+    counts the calls."""
+    return {f"{name}_{k}": 0 for k in ("num_queries", "num_searches", "search_latency", "collect_latency",
+                                       "total_query_latency")}
 
 
 def _is_torch(x) -> bool:
@@ -114,7 +124,7 @@ class DiffCacheGPU:
             device = torch.cuda.current_device()
         self.device = int(device)
         self.name = opts["name"]
-        self.metrics = {f"{self.name}_num_queries": 0}
+        self.metrics = _metric_names(self.name)
         self._lib = _lib.load()
         handle = ctypes.c_void_p()
         _lib.check(self._lib.dc_create(bsz, q_head_num, kv_head_num, head_dim, int(opts["max_ctx_len"]), self.dtype,
@@ -206,9 +216,12 @@ class DiffCacheGPU:
                 _require_contiguous(x, what)
                 if _shape(x) != (self.bsz, self.kv_head_num, ef_c):
                     raise ValueError(f"{what} shape {_shape(x)} != (bsz, kv_head_num, {ef_c})")
+        t0 = time.perf_counter()
         _lib.check(self._lib.dc_query(self._h, _ptr(queries), int(ef), _ptr(out_keys), _ptr(out_vals), _ptr(out_idx),
                                       _ptr(out_bits), _current_stream(stream)))
-        self.metrics[f"{self.name}_num_queries"] += 1
+        # wall time of the call, as the reference measures it (lib.rs:378,403); with device outputs the call only
+        # enqueues work, so device time has to come from set_phase_timing / phase_times
+        self._count_query(int((time.perf_counter() - t0) * 1e6))
 
     def query_streaming(self, cuda_stream: int, out_keys_gpu: int, out_vals_gpu: int, queries, ef: int) -> None:
         """lib.rs:626-636: raw ``CUstream`` / device pointers as integers.  The reference
@@ -217,6 +230,12 @@ class DiffCacheGPU:
         _require_u16(queries, "queries")
         _lib.check(self._lib.dc_query(self._h, _ptr(queries), int(ef), int(out_keys_gpu), int(out_vals_gpu), None, None,
                                       int(cuda_stream)))
+
+    def _count_query(self, total_us: int = 0) -> None:
+        m, n = self.metrics, self.name
+        m[f"{n}_num_queries"] += 1
+        m[f"{n}_num_searches"] += self.bsz * self.kv_head_num   # one search per (batch, kv head), nsw.rs:595
+        m[f"{n}_total_query_latency"] += total_us
 
     def get_keys(self) -> np.ndarray:
         """lib.rs:646-649: stored keys as float32 ``(bsz, kv_head_num, ctx_len, head_dim)``."""
@@ -273,6 +292,38 @@ class DiffCacheGPU:
         _lib.check(self._lib.dc_decode_attend_strided(self._h, _ptr(q), qsb, _ptr(k_new), _ptr(v_new), nsb, _ptr(res_k),
                                                       _ptr(res_v), sb, sh, int(res_len), int(topk), float(scale),
                                                       _ptr(out), _ptr(out_idx), _ptr(out_lse), _current_stream(stream)))
+        self._count_query()
+
+    def window_push(self, k_new, v_new, res_k, res_v, window_state, stream=None) -> None:
+        """Append the step's new token to this layer's window ring (see ``dc_window_push``): the oldest
+        token is spilled into the scanned store once the window is full.  ``window_state`` is the int32
+        device tensor of 8 words shared by all layers."""
+        nsb = self._batch_stride(k_new, self.kv_head_num, "k_new")
+        if self._batch_stride(v_new, self.kv_head_num, "v_new") != nsb:
+            raise ValueError("k_new and v_new must have the same batch stride")
+        st = tuple(res_k.stride())
+        if st != tuple(res_v.stride()) or st[3] != 1 or st[2] != self.head_dim:
+            raise ValueError("res_k/res_v must share strides with contiguous rows of head_dim")
+        _lib.check(self._lib.dc_window_push(self._h, _ptr(k_new), _ptr(v_new), nsb, _ptr(res_k), _ptr(res_v), st[0], st[1],
+                                            _ptr(window_state), _current_stream(stream)))
+
+    def window_advance(self, window_state, stream=None) -> None:
+        """Once per decode step, after the last layer's ``window_push``."""
+        _lib.check(self._lib.dc_window_advance(_ptr(window_state), _current_stream(stream)))
+
+    def decode_attend_dyn(self, q, out, topk: int, res_k, res_v, res_len_dev, res_cap: int, scale: float = 0.0,
+                          out_idx=None, out_lse=None, stream=None) -> None:
+        """``decode_attend`` with the resident length (``res_len_dev``, one int32 on the device) and the
+        stored row count read on the device when the kernels run, so a captured graph of this call stays
+        valid while the window and the store grow.  The new token must already be in the window."""
+        qsb = self._batch_stride(q, self.q_head_num, "q")
+        st = tuple(res_k.stride())
+        if st != tuple(res_v.stride()) or st[3] != 1 or st[2] != self.head_dim:
+            raise ValueError("res_k/res_v must share strides with contiguous rows of head_dim")
+        _lib.check(self._lib.dc_decode_attend_dyn(self._h, _ptr(q), qsb, _ptr(res_k), _ptr(res_v), st[0], st[1],
+                                                  _ptr(res_len_dev), int(res_cap), int(topk), float(scale), _ptr(out),
+                                                  _ptr(out_idx), _ptr(out_lse), _current_stream(stream)))
+        self._count_query()
 
     def _batch_stride(self, t, heads: int, what: str) -> int:
         """0 for a dense ``(bsz, heads, head_dim)`` tensor, else its batch stride in elements."""
@@ -308,6 +359,12 @@ class DiffCacheGPU:
         a, b, c, n = ctypes.c_float(), ctypes.c_float(), ctypes.c_float(), ctypes.c_int()
         _lib.check(self._lib.dc_get_phase_times(self._h, ctypes.byref(a), ctypes.byref(b), ctypes.byref(c),
                                                 ctypes.byref(n)))
+        # the device-timed phases under the reference's counter names: search = scan + select (nsw.rs:597-618),
+        # collect = gather + attention of the selected rows (nsw.rs:620-629 and the attention that follows)
+        m, nm = self.metrics, self.name
+        m[f"{nm}_search_latency"] += int((a.value + b.value) * 1e3)
+        m[f"{nm}_collect_latency"] += int(c.value * 1e3)
+        m[f"{nm}_total_query_latency"] += int((a.value + b.value + c.value) * 1e3)
         return {"steps": n.value, "scan_ms": a.value, "select_ms": b.value, "attend_ms": c.value}
 
     def local_topk(self, q, topk: int, out_bits, out_gidx, stream=None) -> None:

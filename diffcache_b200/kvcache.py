@@ -9,11 +9,23 @@ so the query never leaves the device:
 
 * ``prefill_update_kv_cache`` ingests the middle region device-to-device straight from the
   model's ``(B, S, Hkv, D)`` layout (no ``.cpu().numpy()``, no CAGRA graph build);
-* ``decode_pre_query_operation`` only remembers the query tensor (no D2H copy);
+* ``decode_pre_query_operation`` copies the query into a persistent device buffer (the
+  reference's pinned ``qbuf_cpu``, without the D2H hop), so it can sit inside a captured graph;
 * ``decode_query_kvcache`` + ``decode_post_query_operation`` reproduce the reference's
   two-call shape (retrieved rows land in ``kbuf[:, :, budget-ef:budget]``) for callers that
   still run their own attention kernel;
 * ``decode_attention`` is the fused replacement for query + copy + ``flash_attn_with_kvcache``.
+
+CUDA graphs.  The reference captures, per layer, one graph ending in ``decode_pre_query_operation``
+and one starting with ``decode_post_query_operation`` (src/diffcache/base.py:116-155) and calls
+``decode_query_kvcache`` between their replays; both methods here only enqueue copies between
+buffers allocated before capture, so that pattern keeps working.  ``decode_attention`` can be
+captured once per layer for the whole generation: every length it depends on (rows in the store,
+resident rows, the slot of the new token) lives in device words that its kernels read when they
+run.  The suffix region is a ring there: when it is full, the oldest generated token moves into
+the scanned store and the new one takes its slot (the reference asserts instead,
+diffcache.py:221).  Host attributes (``kvbuf_suffix_len``, ``retrieval_region_len``) follow calls
+made from Python; after graph replays ``sync_lengths()`` refreshes them from the device.
 """
 from __future__ import annotations
 
@@ -72,10 +84,15 @@ class DiffCache:
         shape = (batch_size, num_kv_heads, buf_len, head_dim)
         self.kbuf = [torch.empty(shape, device=self.device, dtype=self.torch_dtype) for _ in range(num_layers)]
         self.vbuf = [torch.empty(shape, device=self.device, dtype=self.torch_dtype) for _ in range(num_layers)]
-        # contiguous landing zone for the two-call query shape (the reference's pinned kbuf_cpu)
+        # contiguous landing zone for the two-call query shape (the reference's pinned kbuf_cpu), allocated
+        # when the retrieval length is known (end of prefill / load), i.e. before any graph capture
         self._stage_k = None
         self._stage_v = None
-        self._queries = None
+        # the reference's qbuf: decode_pre_query_operation copies into it, also when captured
+        self._qbuf = torch.empty((batch_size, num_q_heads, head_dim), device=self.device, dtype=self.torch_dtype)
+        # window-ring state read by the kernels of decode_attention:
+        # {suffix_len, head, prefix_len, cap, res_len_now, steps, 0, 0}
+        self._win = torch.zeros(8, dtype=torch.int32, device=self.device)
 
         self.data_layers = [
             DiffCacheGPU(
@@ -122,7 +139,25 @@ class DiffCache:
         # (B, S', Hkv, D) -> logical (B, Hkv, S', D) view; the engine ingests it with strides
         self.data_layers[layer_idx].prefill(mid_k.permute(0, 2, 1, 3), mid_v.permute(0, 2, 1, 3), None)
         self.retrieval_region_len = mid_k.size(1)
+        self._after_prefill()
         return key_states, value_states
+
+    def _after_prefill(self) -> None:
+        """Lengths are known: size the staging buffers and set the device-side window state."""
+        ef = self._retrieval_len()
+        if ef > 0 and (self._stage_k is None or self._stage_k.size(2) != ef):
+            shape = (self.batch_size, self.num_kv_heads, ef, self.head_dim)
+            self._stage_k = torch.empty(shape, device=self.device, dtype=self.torch_dtype)
+            self._stage_v = torch.empty(shape, device=self.device, dtype=self.torch_dtype)
+        p, sfx = self.kvbuf_prefix_len, self.kvbuf_suffix_len
+        self._win.copy_(torch.tensor([sfx, 0, p, self.kvbuf_suffix_maxlen, p + sfx, 0, 0, 0], dtype=torch.int32))
+
+    def sync_lengths(self) -> None:
+        """Refresh the host attributes from the device words (after replays of a captured
+        ``decode_attention`` graph, which advance the lengths without running any Python)."""
+        w = self._win.cpu().tolist()
+        self.kvbuf_suffix_len = int(w[0])
+        self.retrieval_region_len = int(self.data_layers[0].ctx_len)
 
     # ---- views ---------------------------------------------------------------------------------
     def _retrieval_len(self) -> int:
@@ -141,21 +176,22 @@ class DiffCache:
 
     # ---- decode: the reference's three-call shape -------------------------------------------------
     def decode_pre_query_operation(self, queries: torch.Tensor) -> None:
-        """diffcache.py:191-194 without the device->host hop: the group mean is formed inside
-        the scan kernel, so only the tensor is remembered."""
-        self._queries = queries.view(self.batch_size, self.num_q_heads, self.head_dim)
+        """diffcache.py:191-194 without the device->host hop: the query heads are copied into the
+        persistent query buffer (the group mean is formed later, next to the scan).  The copy is an
+        ordinary stream operation, so it is recorded when this call sits inside a graph capture
+        (base.py:121-125) and every replay delivers that layer's fresh query."""
+        self._qbuf.copy_(queries.view(self.batch_size, self.num_q_heads, self.head_dim), non_blocking=True)
 
     def decode_query_kvcache(self, layer_idx: int) -> None:
-        """diffcache.py:211-223: top-``retrieval_len`` rows of this layer into the staging buffers."""
+        """diffcache.py:211-223: top-``retrieval_len`` rows of this layer into the staging buffers.
+        Called between the replays of the two per-layer graphs, like the reference's engine call."""
         ef = self._retrieval_len()
         if ef > 0:
             group = self.num_q_heads // self.num_kv_heads
-            q = self._queries.view(self.batch_size, self.num_kv_heads, group, self.head_dim)
+            q = self._qbuf.view(self.batch_size, self.num_kv_heads, group, self.head_dim)
             q_mean = q.mean(dim=2).contiguous()
             if self._stage_k is None or self._stage_k.size(2) != ef:
-                shape = (self.batch_size, self.num_kv_heads, ef, self.head_dim)
-                self._stage_k = torch.empty(shape, device=self.device, dtype=self.torch_dtype)
-                self._stage_v = torch.empty(shape, device=self.device, dtype=self.torch_dtype)
+                self._after_prefill()
             self.data_layers[layer_idx].query(self._stage_k, self._stage_v, q_mean, ef)
         assert self.kvbuf_suffix_len < self.kvbuf_suffix_maxlen
         if layer_idx == self.num_layers - 1:
@@ -166,6 +202,10 @@ class DiffCache:
         ef = self._retrieval_len()
         if ef <= 0:
             return
+        if self._stage_k is None or self._stage_k.size(2) != ef:
+            if torch.cuda.is_current_stream_capturing():
+                raise RuntimeError("decode_post_query_operation captured before prefill / load_prefill_cache")
+            self._after_prefill()
         b = self.retrieval_budget
         self.kbuf[layer_idx][:, :, b - ef:b].copy_(self._stage_k[:, :, :ef], non_blocking=True)
         self.vbuf[layer_idx][:, :, b - ef:b].copy_(self._stage_v[:, :, :ef], non_blocking=True)
@@ -177,20 +217,29 @@ class DiffCache:
         the ``flash_attn_with_kvcache`` call of base.py:134-142).  ``queries`` ``(bsz, 1, Hq*D)`` or
         ``(bsz, Hq, D)``; ``k_new/v_new`` ``(bsz, 1, Hkv, D)`` or ``(bsz, Hkv, D)``: the new token is
         appended to the suffix region in place and attended.  The suffix length is advanced after
-        the last layer, like the reference."""
+        the last layer, like the reference; when the suffix region is full, the oldest generated
+        token moves into the scanned store and the new one takes its slot.
+
+        The call may be captured in a CUDA graph (one per layer, inputs in static tensors) and
+        replayed for every generated token: the lengths it works with are device words."""
         q = queries.reshape(self.batch_size, self.num_q_heads, self.head_dim)
         kn = k_new.reshape(self.batch_size, self.num_kv_heads, self.head_dim)
         vn = v_new.reshape(self.batch_size, self.num_kv_heads, self.head_dim)
         if out is None:
             out = torch.empty_like(q)
-        assert self.kvbuf_suffix_len < self.kvbuf_suffix_maxlen
         b = self.retrieval_budget
-        res_len = self.kvbuf_prefix_len + self.kvbuf_suffix_len
-        self.data_layers[layer_idx].decode_attend(
-            q, out, topk=self._retrieval_len(), res_k=self.kbuf[layer_idx][:, :, b:], res_v=self.vbuf[layer_idx][:, :, b:],
-            res_len=res_len, k_new=kn, v_new=vn, out_idx=out_idx)
+        eng = self.data_layers[layer_idx]
+        res_k, res_v = self.kbuf[layer_idx][:, :, b:], self.vbuf[layer_idx][:, :, b:]
+        eng.window_push(kn, vn, res_k, res_v, self._win)
+        eng.decode_attend_dyn(q, out, topk=self._retrieval_len(), res_k=res_k, res_v=res_v, res_len_dev=self._win[4:5],
+                              res_cap=self.kvbuf_prefix_len + self.kvbuf_suffix_maxlen, out_idx=out_idx)
         if layer_idx == self.num_layers - 1:
-            self.kvbuf_suffix_len += 1
+            eng.window_advance(self._win)
+            # host mirrors of what the kernels just did (exact for calls made from Python)
+            if self.kvbuf_suffix_len < self.kvbuf_suffix_maxlen:
+                self.kvbuf_suffix_len += 1
+            elif self.retrieval_region_len < self.max_length:
+                self.retrieval_region_len += 1
         return out
 
     # ---- prefill cache (checkpoint) ----------------------------------------------------------------
@@ -234,3 +283,4 @@ class DiffCache:
                 self.kbuf[layer_idx][:, :, lo:hi, :] = torch.load(os.path.join(layer_path, "k.pt"))
                 self.vbuf[layer_idx][:, :, lo:hi, :] = torch.load(os.path.join(layer_path, "v.pt"))
             self.data_layers[layer_idx].load(os.path.join(prefill_cache_path, f"d_l_{layer_idx:03d}"), ctx_len)
+        self._after_prefill()

@@ -74,10 +74,13 @@ class PQWorkspace:
 
 
 def adc_rerank_topk(keys: torch.Tensor, codes: torch.Tensor, centroids: torch.Tensor, q: torch.Tensor, group: int,
-                    n_cand: int, topk: int, ws: PQWorkspace | None = None, dtype: int = 0):
+                    n_cand: int, topk: int, ws: PQWorkspace | None = None, dtype: int = 0, mark=None):
     """One PQ retrieval: returns ``(sel_idx, sel_bits)`` ``(P, topk)`` int32 tensors holding the
     selected row ids (best first) and their exact ranking keys.  keys ``(P, n, D)``; codes
-    ``(P, n, n_sub)``; q ``(B, Hq, D)`` query heads (group mean formed in the kernels)."""
+    ``(P, n, n_sub)``; q ``(B, Hq, D)`` query heads (group mean formed in the kernels).  ``mark``
+    (optional callable) is called after every stage: table, ADC scan, candidate select, rerank, final
+    select — for per-stage timing."""
+    mark = mark or (lambda: None)
     lib = _lib.load()
     P, n, D = keys.shape
     n_sub = codes.shape[2]
@@ -86,12 +89,17 @@ def adc_rerank_topk(keys: torch.Tensor, codes: torch.Tensor, centroids: torch.Te
     ws.minmax.copy_(ws.minmax_init)
     _lib.check(lib.dc_pq_build_lut(q.data_ptr(), 1, group, dtype, centroids.data_ptr(), P, D, n_sub,
                                    ws.lut.data_ptr(), st))
+    mark()
     _lib.check(lib.dc_pq_adc_scan(codes.data_ptr(), n * n_sub, P, n, n_sub, ws.lut.data_ptr(), ws.scores.data_ptr(),
                                   n, ws.minmax.data_ptr(), st))
+    mark()
     _lib.check(lib.dc_topk_select(ws.scores.data_ptr(), None, n, P, n, n_cand, ws.minmax.data_ptr(), None,
                                   ws.cand_idx.data_ptr(), n_cand, ws.status.data_ptr(), st))
+    mark()
     _lib.check(lib.dc_rerank_scores(keys.data_ptr(), n * D, P, D, dtype, q.data_ptr(), 1, group,
                                     ws.cand_idx.data_ptr(), n_cand, n_cand, ws.cand_bits.data_ptr(), st))
+    mark()
     _lib.check(lib.dc_topk_select(ws.cand_bits.data_ptr(), ws.cand_idx.data_ptr(), n_cand, P, n_cand, topk, None,
                                   ws.sel_bits.data_ptr(), ws.sel_idx.data_ptr(), topk, ws.status.data_ptr(), st))
+    mark()
     return ws.sel_idx, ws.sel_bits

@@ -19,7 +19,8 @@ gather layouts, offsets) can be exercised on CPU ranks over gloo with a stand-in
 """
 from __future__ import annotations
 
-from typing import List, Optional, Tuple
+import ctypes
+from typing import List, Optional, Sequence, Tuple
 
 import torch
 import torch.distributed as dist
@@ -27,6 +28,109 @@ import torch.distributed as dist
 from . import _lib
 
 PAD = 0xFFFFFFFF
+
+
+class PeerExchange:
+    """Exchange buffers of all ranks mapped into one another (CUDA IPC over ``torch.distributed``), for the
+    fused exchange kernels behind ``dc_xchg_*`` / ``dc_sharded_*``: producers store their block into every
+    peer's buffer over NVLink and raise a flag, consumers poll their own buffer.  ``slot_bytes[c]`` is the
+    block size of channel ``c`` per rank (multiples of 16).
+
+    Construction is collective.  If any rank cannot map a peer (no peer access, IPC not permitted) every
+    rank raises ``RuntimeError`` and the caller keeps using the NCCL all-gathers."""
+
+    def __init__(self, slot_bytes: Sequence[int], device: int, group: Optional["dist.ProcessGroup"] = None,
+                 _rank_world: Optional[Tuple[int, int]] = None):
+        self.lib = _lib.load()
+        if _rank_world is not None:   # wired by in_process()
+            self.rank, self.world = _rank_world
+        else:
+            self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+            self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.device = int(device)
+        self.slot_bytes = [int(b) for b in slot_bytes]
+        arr = (ctypes.c_int64 * len(self.slot_bytes))(*self.slot_bytes)
+        handle = ctypes.c_void_p()
+        _lib.check(self.lib.dc_xchg_create(self.rank, self.world, self.device, arr, len(self.slot_bytes),
+                                           ctypes.byref(handle)))
+        self._h = handle
+        if self.world > 1 and _rank_world is None:
+            ok, why = 1, ""
+            try:
+                mine = ctypes.create_string_buffer(self.lib.dc_xchg_handle_bytes())
+                _lib.check(self.lib.dc_xchg_get_handle(self._h, mine))
+                handles = [None] * self.world
+                dist.all_gather_object(handles, bytes(mine.raw), group=group)
+                for r, raw in enumerate(handles):
+                    if r != self.rank:
+                        _lib.check(self.lib.dc_xchg_open_peer(self._h, r, raw))
+            except Exception as exc:  # keep going to the collective vote below
+                ok, why = 0, str(exc)
+            vote = torch.tensor([ok], dtype=torch.int32, device=torch.device("cuda", self.device))
+            dist.all_reduce(vote, op=dist.ReduceOp.MIN, group=group)
+            if int(vote[0]) == 0:
+                self.close()
+                raise RuntimeError(f"peer exchange unavailable on at least one rank ({why or 'another rank failed'})")
+            dist.barrier(group)
+
+    @classmethod
+    def in_process(cls, slot_bytes: Sequence[int], devices: Sequence[int]) -> List["PeerExchange"]:
+        """One exchange per entry of ``devices``, all owned by this process and wired to one another by plain
+        pointers (no IPC): several GPUs driven by one process, or several ranks emulated on one GPU.  With
+        emulated ranks the caller must run the ranks phase by phase (all pushes of a phase before any wait
+        for it): kernels of one GPU that wait for one another cannot be relied on to run concurrently."""
+        world = len(devices)
+        xs = [cls(slot_bytes, devices[r], _rank_world=(r, world)) for r in range(world)]
+        for a in xs:
+            for b in xs:
+                if a is not b:
+                    _lib.check(a.lib.dc_xchg_set_peer(a._h, b.rank, a.lib.dc_xchg_local(b._h)))
+        return xs
+
+    def channel_tensor(self, channel: int, dtype: torch.dtype) -> torch.Tensor:
+        """This rank's copy of a channel as a ``(world, slot_elems)`` tensor (no copy)."""
+        ptr = self.lib.dc_xchg_channel(self._h, channel)
+        n16 = self.slot_bytes[channel] // 2
+
+        class _Raw:
+            __cuda_array_interface__ = {"shape": (self.world, n16), "typestr": "<i2", "data": (int(ptr), False),
+                                        "version": 2}
+
+        t = torch.as_tensor(_Raw(), device=torch.device("cuda", self.device))
+        return t.view(dtype)
+
+    def push(self, channel: int, src: torch.Tensor, stream=None) -> None:
+        st = int(torch.cuda.current_stream().cuda_stream) if stream is None else int(stream)
+        _lib.check(self.lib.dc_xchg_push(self._h, channel, src.data_ptr(), src.numel() * src.element_size(), st))
+
+    def push_rows(self, channel: int, src: torch.Tensor, stream=None) -> None:
+        """``src`` ``(rows, n)`` contiguous: afterwards every rank's channel reads ``(rows, world, n)``."""
+        st = int(torch.cuda.current_stream().cuda_stream) if stream is None else int(stream)
+        rows = src.shape[0]
+        _lib.check(self.lib.dc_xchg_push_rows(self._h, channel, src.data_ptr(), rows,
+                                              src.numel() // rows * src.element_size(), st))
+
+    def wait(self, channel: int, stream=None) -> None:
+        st = int(torch.cuda.current_stream().cuda_stream) if stream is None else int(stream)
+        _lib.check(self.lib.dc_xchg_wait(self._h, channel, st))
+
+    def check(self) -> None:
+        """Synchronises the current stream; raises if a wait for peer data ran out of time."""
+        _lib.check(self.lib.dc_xchg_check(self._h, int(torch.cuda.current_stream().cuda_stream)))
+
+    def set_timeout_ms(self, ms: int) -> None:
+        _lib.check(self.lib.dc_xchg_set_timeout_ms(self._h, int(ms)))
+
+    def close(self) -> None:
+        h, self._h = getattr(self, "_h", None), None
+        if h:
+            self.lib.dc_xchg_destroy(h)
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
 
 
 def shard_rows(n_rows: int, world: int) -> List[Tuple[int, int]]:
@@ -83,12 +187,25 @@ class SequenceShardedStep:
     followed by the (max, sum) pairs
     """
 
-    def __init__(self, backend, topk: int, group: Optional["dist.ProcessGroup"] = None):
+    def __init__(self, backend, topk: int, group: Optional["dist.ProcessGroup"] = None, exchange: str = "nccl"):
+        """``exchange``: "nccl" — two ``all_gather_into_tensor`` calls per step; "peer" — the exchanges are
+        done by the step's own kernels with stores over NVLink (:class:`PeerExchange`; GPU backend only, the
+        whole step is one C call); "auto" — "peer" when it can be set up, else "nccl"."""
         self.backend = backend
         self.topk = topk
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.xchg = None
+        if exchange in ("peer", "auto") and hasattr(backend, "make_exchange"):
+            try:
+                self.xchg = backend.make_exchange(topk, group)
+            except RuntimeError:
+                if exchange == "peer":
+                    raise
+        elif exchange == "peer":
+            raise ValueError("the peer exchange needs the GPU backend")
+        self.exchange = "peer" if self.xchg is not None else "nccl"
 
     def _all_gather(self, t: torch.Tensor) -> torch.Tensor:
         if self.world == 1:
@@ -111,6 +228,8 @@ class SequenceShardedStep:
         also exchange the ids and run the full merge select, which leaves the global row list, identical
         on all ranks, in ``last_selection``."""
         k = self.topk
+        if self.xchg is not None and not want_selection:
+            return self.backend.peer_step(q, k, self.xchg)               # seven kernels, no collective call
         bits, gidx = self.backend.local_topk(q, k)                       # (P, k) each, ascending, padded
         P = bits.shape[0]
         use_prefix = self.world * k * 4 <= self.PREFIX_MERGE_MAX_BYTES and hasattr(self.backend, "merge_count")
@@ -165,6 +284,53 @@ class GpuShardBackend:
     @staticmethod
     def _stream() -> int:
         return int(torch.cuda.current_stream().cuda_stream)
+
+    def make_exchange(self, topk: int, group=None) -> PeerExchange:
+        need = (ctypes.c_int64 * 2)()
+        _lib.check(self.lib.dc_sharded_slot_bytes(self.e._h, int(topk), need))
+        return PeerExchange([int(need[0]), int(need[1])], self.e.device, group)
+
+    def _res_args(self):
+        sb = sh = 0
+        if self.res_k is not None:
+            st = tuple(self.res_k.stride())
+            sb, sh = st[0], st[1]
+        ptr = lambda t: None if t is None else t.data_ptr()  # noqa: E731
+        return ptr(self.k_new), ptr(self.v_new), ptr(self.res_k), ptr(self.res_v), sb, sh, int(self.res_len)
+
+    def peer_step(self, q, k, xchg: PeerExchange):
+        """The whole step as one call: scan, select, key push | wait, prefix count, attention, partial push |
+        wait, merge."""
+        out = self._buf("out", (self.e.bsz, self.e.q_head_num, self.D), torch.bfloat16 if self.e.dtype == 0 else torch.float16)
+        kn, vn, rk, rv, sb, sh, rl = self._res_args()
+        _lib.check(self.lib.dc_sharded_decode_attend(self.e._h, xchg._h, q.data_ptr(), kn, vn, rk, rv, sb, sh, rl, int(k),
+                                                     float(self.scale), out.data_ptr(), None, self._stream()))
+        return out
+
+    def peer_phase(self, phase: int, q, k, xchg: PeerExchange):
+        """One of the three phases of :meth:`peer_step` (0 local, 1 attend, 2 combine), for drivers that
+        hold several ranks in one process and must run them phase by phase."""
+        if phase == 0:
+            _lib.check(self.lib.dc_sharded_local(self.e._h, xchg._h, q.data_ptr(), int(k), self._stream()))
+            return None
+        if phase == 1:
+            kn, vn, rk, rv, sb, sh, rl = self._res_args()
+            _lib.check(self.lib.dc_sharded_attend(self.e._h, xchg._h, q.data_ptr(), kn, vn, rk, rv, sb, sh, rl,
+                                                  float(self.scale), self._stream()))
+            return None
+        out = self._buf("out", (self.e.bsz, self.e.q_head_num, self.D), torch.bfloat16 if self.e.dtype == 0 else torch.float16)
+        _lib.check(self.lib.dc_sharded_combine(self.e._h, xchg._h, out.data_ptr(), None, self._stream()))
+        return out
+
+    def trace_step(self, q, k, xchg: PeerExchange):
+        """One peer step with an event after every kernel; returns the intervals in microseconds, in order:
+        scan, select, key push, wait + prefix count, attention + split merge, partial push, wait + merge."""
+        _lib.check(self.lib.dc_trace_begin(self.e._h, 16))
+        self.peer_step(q, k, xchg)
+        vals = (ctypes.c_float * 16)()
+        n = ctypes.c_int()
+        _lib.check(self.lib.dc_trace_read(self.e._h, vals, ctypes.byref(n)))
+        return [vals[i] * 1e3 for i in range(max(0, n.value - 1))]
 
     def local_topk(self, q, k):
         both = self._buf("cand", (2, self.P, k), torch.int32)

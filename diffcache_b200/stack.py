@@ -11,7 +11,11 @@ With ``world > 1`` the stack is sharded by KV head: rank r owns kv heads
 ``[r*Hkv/world, (r+1)*Hkv/world)`` of every layer, the matching query heads and the matching
 rows of the fused projection, so scan / select / attend are local; the per-layer exchange is one
 all-gather of the attention output slice ``(B, Hq/world * D)`` before a replicated output
-projection (deterministic: every rank computes the same residual stream).
+projection (deterministic: every rank computes the same residual stream).  That all-gather is
+either an NCCL call or (``exchange="peer"``) a push of the slice into every rank's buffer with
+stores over NVLink, interleaved so that the buffer reads ``(B, Hq*D)`` directly, plus a small wait
+kernel (:class:`diffcache_b200.sharded.PeerExchange`); consecutive layers use different channels of
+the exchange so that a fast rank never overwrites a block a slow rank is still reading.
 """
 from __future__ import annotations
 
@@ -23,15 +27,16 @@ import torch.nn.functional as F
 
 from . import synth
 from .engine import DiffCacheGPU
-from .sharded import shard_heads
+from .sharded import PeerExchange, shard_heads
 
 
 class AttentionStack:
     def __init__(self, n_layers: int, hidden: int, batch: int, q_heads: int, kv_heads: int, head_dim: int,
                  context: int, topk: int, sink: int, window: int, dtype: str = "bf16", seed: int = 2000,
                  device: Optional[torch.device] = None, group: Optional["dist.ProcessGroup"] = None,
-                 unsharded: bool = False):
-        """``unsharded=True`` builds the whole stack on this device even inside a process group."""
+                 unsharded: bool = False, exchange: str = "nccl"):
+        """``unsharded=True`` builds the whole stack on this device even inside a process group.
+        ``exchange``: "nccl", "peer" or "auto" (peer when it can be set up)."""
         use_dist = dist.is_initialized() and not unsharded
         self.world = dist.get_world_size(group) if use_dist else 1
         self.rank = dist.get_rank(group) if use_dist else 0
@@ -78,14 +83,34 @@ class AttentionStack:
             del k, v
         self.attn_local = torch.empty((batch, self.q_local, head_dim), dtype=dt, device=self.device)
         self.attn_full = torch.empty((self.world, batch, self.q_local * head_dim), dtype=dt, device=self.device)
+        # Peer exchange: m channels used round-robin, m chosen so that the last layer of one step and the first
+        # layer of the next (channel 0 again when the step is replayed from a graph) never share a channel.
+        self.xchg, self.xchg_channels, self.xchg_views = None, 0, []
+        if self.world > 1 and exchange in ("peer", "auto"):
+            m = next((c for c in (2, 3, 4) if n_layers > 1 and (n_layers - 1) % c != 0), 0)
+            if m == 0 and exchange == "peer":
+                raise ValueError("the peer exchange needs at least two layers")
+            if m:
+                try:
+                    slot = batch * self.q_local * head_dim * 2
+                    self.xchg = PeerExchange([slot] * m, self.device.index, group)
+                    self.xchg_channels = m
+                    self.xchg_views = [self.xchg.channel_tensor(c, dt).view(batch, self.world * self.q_local * head_dim)
+                                       for c in range(m)]
+                except RuntimeError:
+                    if exchange == "peer":
+                        raise
+        self.exchange = "peer" if self.xchg is not None else ("nccl" if self.world > 1 else "none")
+        self._last_channel = -1
         torch.cuda.synchronize(self.device)
 
-    def step(self, x: torch.Tensor) -> torch.Tensor:
-        """x ``(batch, hidden)`` -> ``(batch, hidden)`` after all layers.  The resident length is not
-        advanced, so repeated calls time the same step."""
+    def step(self, x: torch.Tensor, n_layers: Optional[int] = None, probe: Optional[dict] = None) -> torch.Tensor:
+        """x ``(batch, hidden)`` -> ``(batch, hidden)`` after ``n_layers`` (default: all) layers.  The resident
+        length is not advanced, so repeated calls time the same step.  ``probe`` (a dict) receives layer 0's
+        query heads, new key/value rows and local attention output, for checks by the caller."""
         B, D = self.batch, self.head_dim
         nq, nkv = self.q_local * D, self.kv_local * D
-        for layer in range(self.n_layers):
+        for layer in range(self.n_layers if n_layers is None else n_layers):
             h = F.rms_norm(x, (self.hidden,), self.norm_w[layer], 1e-5)
             qkv = F.linear(h, self.wqkv[layer])
             # slices of the fused projection output, passed as they are (batch stride = nq + 2*nkv)
@@ -94,7 +119,22 @@ class AttentionStack:
             vn = qkv[:, nq + nkv:].unflatten(1, (self.kv_local, D))
             self.engines[layer].decode_attend(q, self.attn_local, self.topk, res_k=self.res_k[layer],
                                               res_v=self.res_v[layer], res_len=self.res_rows, k_new=kn, v_new=vn)
-            if self.world > 1:
+            if probe is not None and layer == 0:
+                probe.update(q=q.clone(), k_new=kn.clone(), v_new=vn.clone(), attn=self.attn_local.clone())
+            if self.xchg is not None:
+                ch = layer % self.xchg_channels
+                if ch == self._last_channel:
+                    # two pushes in a row on one channel (a call that stopped after an odd number of layers):
+                    # make sure every rank has finished reading the block this push overwrites
+                    if torch.cuda.is_current_stream_capturing():
+                        raise RuntimeError("consecutive pushes on one exchange channel cannot be captured")
+                    torch.cuda.synchronize(self.device)
+                    dist.barrier(self.pg)
+                self._last_channel = ch
+                self.xchg.push_rows(ch, self.attn_local.view(B, -1))   # lands as (B, world, q_local*D) on every rank
+                self.xchg.wait(ch)
+                attn = self.xchg_views[ch]
+            elif self.world > 1:
                 dist.all_gather_into_tensor(self.attn_full.view(-1), self.attn_local.view(-1), group=self.pg)
                 attn = self.attn_full.view(self.world, B, self.kv_local, -1).permute(1, 0, 2, 3).reshape(B, -1)
             else:
@@ -106,3 +146,7 @@ class AttentionStack:
         for e in self.engines:
             e.close()
         self.engines = []
+        if self.xchg is not None:
+            self.xchg_views = []
+            self.xchg.close()
+            self.xchg = None

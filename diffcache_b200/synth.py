@@ -91,6 +91,37 @@ def make_kv(batch: int, kv_heads: int, n: int, head_dim: int, seed: int, dtype: 
     return k, v
 
 
+ROW_CHUNK = 1 << 16
+
+
+def make_kv_rows(batch: int, kv_heads: int, row_start: int, n_rows: int, head_dim: int, seed: int, dtype: str,
+                 device="cpu", total: int | None = None):
+    """Rows ``[row_start, row_start + n_rows)`` of a sequence of ``total`` tokens whose contents depend only on
+    (seed, global row), not on how the sequence is cut: every 65536-row chunk has its own generator seed, so
+    ranks that hold different row ranges of one sequence generate exactly the rows a single holder would.
+    Same distributions as :func:`make_kv`."""
+    total = row_start + n_rows if total is None else total
+    dev = torch.device(device)
+    dt = torch_dtype(dtype)
+    k = torch.empty((batch, kv_heads, n_rows, head_dim), dtype=dt, device=dev)
+    v = torch.empty((batch, kv_heads, n_rows, head_dim), dtype=dt, device=dev)
+    drift_dir = torch.randn((kv_heads, head_dim), generator=torch.Generator(device=dev).manual_seed(seed), device=dev)
+    first, last = row_start // ROW_CHUNK, (row_start + n_rows - 1) // ROW_CHUNK if n_rows > 0 else -1
+    for c in range(first, last + 1):
+        gen = torch.Generator(device=dev).manual_seed(seed * 1_000_003 + 7 * c + 1)
+        kc = torch.randn((batch, kv_heads, ROW_CHUNK, head_dim), generator=gen, device=dev)
+        vc = torch.randn((batch, kv_heads, ROW_CHUNK, head_dim), generator=gen, device=dev)
+        for ch in OUTLIER_CHANNELS:
+            if ch < head_dim:
+                kc[..., ch] *= 8.0
+        pos = (torch.arange(c * ROW_CHUNK, (c + 1) * ROW_CHUNK, device=dev, dtype=torch.float32)) / float(total) - 0.5
+        kc += 0.5 * pos[None, None, :, None] * drift_dir[None, :, None, :]
+        lo, hi = max(row_start, c * ROW_CHUNK), min(row_start + n_rows, (c + 1) * ROW_CHUNK)
+        k[:, :, lo - row_start:hi - row_start] = kc[:, :, lo - c * ROW_CHUNK:hi - c * ROW_CHUNK].to(dt)
+        v[:, :, lo - row_start:hi - row_start] = vc[:, :, lo - c * ROW_CHUNK:hi - c * ROW_CHUNK].to(dt)
+    return k, v
+
+
 def make_query(keys: torch.Tensor, group: int, seed: int):
     """Query heads ``(batch, kv_heads*group, head_dim)``: 0.3 * a random cached key + N(0,1)."""
     batch, kv_heads, n, head_dim = keys.shape

@@ -96,10 +96,14 @@ int dc_prefill(dc_engine* e, const void* keys, const void* vals, int64_t seq_len
  * Replaces DiffCacheCPU.insert (lib.rs:591-599) → Index::insert (nsw.rs:544-557):
  * appends one row per problem; keys/vals are (bsz, kv_heads, head_dim)
  * contiguous, host or device.  Fails with DC_ESTATE when the store is full.
+ * The row index is read from the engine's device length word when the copy runs
+ * (and the word is advanced there), so an insert captured into a CUDA graph
+ * appends at the right place on every replay.
  */
 int dc_insert(dc_engine* e, const void* keys, const void* vals, uint64_t stream);
 
-/* Number of valid rows per problem (DataLayer.ctx_len, lib.rs:191). */
+/* Number of valid rows per problem (DataLayer.ctx_len, lib.rs:191).  Synchronises the device after
+ * dc_window_push has been used (only the device knows how many rows were spilled into the store). */
 int dc_ctx_len(dc_engine* e, int64_t* out);
 
 /*
@@ -186,6 +190,42 @@ int dc_decode_attend_strided(dc_engine* e, const void* q, int64_t q_stride_b, co
                              void* out, int32_t* out_idx, float* out_lse, uint64_t stream);
 
 /*
+ * Decode loop with every length on the device, so that ONE captured CUDA graph per
+ * layer serves the whole generation (the reference captures two graphs per layer,
+ * src/diffcache/base.py:116-155, and updates `cache_seqlens` between replays).
+ *
+ * window_state is 8 int32 device words shared by all layers of a model:
+ *   {suffix_len, head, prefix_len, cap, res_len_now, steps, 0, 0}
+ * The resident buffer of a (batch, kv head) holds prefix_len sink rows followed by
+ * `cap` window slots (the reference's kvbuf suffix region of kvbuf_suffix_maxlen
+ * rows, src/diffcache/kvcache/diffcache.py:48-66).  The caller initialises
+ * suffix_len, prefix_len and cap (head = 0) after prefill.
+ *
+ * dc_window_push: appends the step's new token to this layer's window.  While the
+ * window is not full it goes to slot suffix_len.  Once it is full the oldest token
+ * (slot head) is first appended to the scanned store — DataLayer::insert
+ * (diffcache_cpu/src/lib.rs:352-369, Index::insert nsw.rs:544-557), which the
+ * reference never calls: it stops at `assert kvbuf_suffix_len < kvbuf_suffix_maxlen`
+ * (diffcache.py:221) — and the new token takes its slot.  Writes res_len_now =
+ * prefix_len + min(suffix_len + 1, cap).  If the store is full too, the oldest
+ * token is dropped and status 302 is recorded (dc_check_status).
+ * dc_window_advance: once per decode step, after the last layer's push: suffix_len
+ * grows until cap, then head moves round the ring (diffcache.py:222-223).
+ * dc_decode_attend_dyn: dc_decode_attend_strided without a new token (it already
+ * sits in the window) and with the resident length read from *res_len_dev when the
+ * kernels run; res_cap (>= any value that word takes) only sizes the launch.  The
+ * number of stored rows is likewise read from the engine's device word.
+ * After dc_window_push the host no longer knows the row count without asking the
+ * device: dc_ctx_len synchronises, and launches are sized for max_ctx_len.
+ */
+int dc_window_push(dc_engine* e, const void* k_new, const void* v_new, int64_t new_stride_b, void* res_k, void* res_v,
+                   int64_t res_stride_b, int64_t res_stride_h, int32_t* window_state, uint64_t stream);
+int dc_window_advance(int32_t* window_state, uint64_t stream);
+int dc_decode_attend_dyn(dc_engine* e, const void* q, int64_t q_stride_b, void* res_k, void* res_v,
+                         int64_t res_stride_b, int64_t res_stride_h, const int32_t* res_len_dev, int res_cap, int topk,
+                         float scale, void* out, int32_t* out_idx, float* out_lse, uint64_t stream);
+
+/*
  * Adaptive retrieval budget.  Replaces the k-check early stop of the reference's
  * search (fit_alpha_from_logits / estimate_top_h_mass / k_check_early_stoppable,
  * diffcache_cpu/src/nsw.rs:198-300, applied at the checkpoints of `k_check_seq`,
@@ -212,6 +252,17 @@ int dc_get_budget(dc_engine* e, int32_t* out, uint64_t stream);
  */
 int dc_set_phase_timing(dc_engine* e, int max_steps);
 int dc_get_phase_times(dc_engine* e, float* scan_ms, float* select_ms, float* attend_ms, int* steps);
+
+/*
+ * Kernel-by-kernel trace of the sequence-sharded step (dc_local_topk / dc_sharded_*): after
+ * dc_trace_begin(e, n) the next calls record a CUDA event on their stream before the scan and after
+ * every kernel they launch (scan, select, key push, prefix count, attention + split merge, partial
+ * push, final merge), up to n events; dc_trace_read synchronises the last one, returns the
+ * *n_marks - 1 intervals between consecutive events in milliseconds and closes the trace.  Same
+ * purpose as dc_set_phase_timing; not usable during graph capture.
+ */
+int dc_trace_begin(dc_engine* e, int max_marks);
+int dc_trace_read(dc_engine* e, float* intervals_ms, int* n_marks);
 
 /* ------------------------------------------------------------------------- *
  * Sequence-sharded decode (one engine per GPU holds a contiguous row range).
@@ -243,6 +294,74 @@ int dc_attend_owned(dc_engine* e, const void* q, const uint32_t* sel_gidx, int n
                     const void* k_new, const void* v_new, void* res_k, void* res_v,
                     int64_t res_stride_b, int64_t res_stride_h, int res_len, float scale,
                     float* out_acc, float* out_ml, const int32_t* sel_count, uint64_t stream);
+
+/* ------------------------------------------------------------------------- *
+ * Peer exchange: the two all-gathers of a sequence-sharded step done by plain
+ * stores over NVLink into buffers the ranks have mapped from one another, fused
+ * with the kernels that consume the data (no collective library, no Python).
+ * No counterpart in the reference (single process, single GPU).
+ *
+ * Set-up, once: every rank calls dc_xchg_create (its own buffer: per channel
+ * `world` slots of slot_bytes[c] bytes, multiples of 16), hands the
+ * dc_xchg_handle_bytes()-byte handle of dc_xchg_get_handle to every other rank
+ * over any side channel (it is a cudaIpcMemHandle_t), and maps each peer with
+ * dc_xchg_open_peer; ranks that live in the same process use dc_xchg_set_peer
+ * with dc_xchg_local() of the peer instead.  All ranks must have finished this
+ * before the first push (a host barrier).
+ *
+ * dc_xchg_push(channel, src, bytes): stores `bytes` (multiple of 16) from device
+ * memory `src` into slot `rank` of the channel in EVERY rank's buffer, then
+ * publishes a new epoch in every rank's flag word for (channel, rank).
+ * dc_xchg_push_rows(channel, src, rows, row_bytes): the same for a (rows,
+ * row_bytes) block that is to be interleaved with the other ranks' blocks row by
+ * row: afterwards the channel reads as (rows, world, row_bytes), i.e. as the
+ * concatenation along the last axis (an all-gather of head slices).
+ * dc_xchg_wait(channel): a kernel that returns once the blocks of the current
+ * epoch of all ranks have arrived in this rank's buffer (dc_xchg_channel gives
+ * the local address: slot r at offset r * slot_bytes).  Every rank must issue
+ * the same sequence of pushes.  Waits are bounded (2 s by default,
+ * dc_xchg_set_timeout_ms or the environment variable DC_XCHG_TIMEOUT_MS): when
+ * one runs out, the kernel records a status and finishes, and dc_xchg_check
+ * (synchronises `stream`) returns DC_EDEVICE — a missing peer never hangs the GPU.
+ * ------------------------------------------------------------------------- */
+typedef struct dc_xchg dc_xchg;
+int dc_xchg_create(int rank, int world, int device, const int64_t* slot_bytes, int n_channels, dc_xchg** out);
+int dc_xchg_destroy(dc_xchg* x);
+int dc_xchg_handle_bytes(void);
+int dc_xchg_get_handle(dc_xchg* x, void* handle_out);
+int dc_xchg_open_peer(dc_xchg* x, int peer_rank, const void* handle);
+int dc_xchg_set_peer(dc_xchg* x, int peer_rank, void* peer_base);
+void* dc_xchg_local(dc_xchg* x);
+void* dc_xchg_channel(dc_xchg* x, int channel);
+int dc_xchg_set_timeout_ms(dc_xchg* x, int ms);
+int dc_xchg_push(dc_xchg* x, int channel, const void* src, int64_t bytes, uint64_t stream);
+int dc_xchg_push_rows(dc_xchg* x, int channel, const void* src, int64_t rows, int64_t row_bytes, uint64_t stream);
+int dc_xchg_wait(dc_xchg* x, int channel, uint64_t stream);
+int dc_xchg_check(dc_xchg* x, uint64_t stream);
+
+/*
+ * One rank's share of a sequence-sharded decode step over a peer exchange whose
+ * channel 0 / channel 1 slots hold at least the two sizes dc_sharded_slot_bytes
+ * reports (candidate keys; partial attention results):
+ *   dc_sharded_local    scan + local top-k of this engine's rows, keys pushed to every rank;
+ *   dc_sharded_attend   waits for all ranks' keys, counts the prefix of this rank's own list that is
+ *                       globally selected (dc_merge_sorted_count), attends over it (dc_attend_owned;
+ *                       resident rows / new token as given there) and pushes the partial result;
+ *   dc_sharded_combine  waits for all ranks' partials and merges them by log-sum-exp into `out`
+ *                       (bsz, q_heads, head_dim), identical on every rank.
+ * dc_sharded_decode_attend runs the three in a row: the whole step is one call and seven kernels on
+ * `stream`, capturable in a CUDA graph once the first call has allocated the per-engine buffers.
+ * Results are those of dc_decode_attend on the concatenated rows (same ranking keys, ties to the
+ * smaller global row id: nsw.rs:74-91,612).
+ */
+int dc_sharded_slot_bytes(dc_engine* e, int topk, int64_t* out2);
+int dc_sharded_local(dc_engine* e, dc_xchg* x, const void* q, int topk, uint64_t stream);
+int dc_sharded_attend(dc_engine* e, dc_xchg* x, const void* q, const void* k_new, const void* v_new, void* res_k,
+                      void* res_v, int64_t res_stride_b, int64_t res_stride_h, int res_len, float scale, uint64_t stream);
+int dc_sharded_combine(dc_engine* e, dc_xchg* x, void* out, float* out_lse, uint64_t stream);
+int dc_sharded_decode_attend(dc_engine* e, dc_xchg* x, const void* q, const void* k_new, const void* v_new, void* res_k,
+                             void* res_v, int64_t res_stride_b, int64_t res_stride_h, int res_len, int topk, float scale,
+                             void* out, float* out_lse, uint64_t stream);
 
 /* ------------------------------------------------------------------------- *
  * Stateless kernels (device pointers only).  The engine calls are compositions

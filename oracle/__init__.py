@@ -131,18 +131,22 @@ def topk(bits: np.ndarray, ef: int, ids: np.ndarray | None = None, method: str =
 
 
 def query(keys_u16, vals_u16, q_mean_u16, ef: int, dtype: int, n: int | None = None, exact: bool = True,
-          n_threads: int = 0, gather: bool = True):
+          n_threads: int = 0, gather: bool = True, out_keys=None, out_vals=None):
     """DataLayer::query, brute force.  keys/vals (n_prob, n_max, D); q_mean (n_prob, D).
 
-    Returns dict(ef, keys, vals, idx, bits) with row i = i-th best."""
+    Returns dict(ef, keys, vals, idx, bits) with row i = i-th best.  ``out_keys``/``out_vals`` (uint16,
+    (n_prob, min(ef, n), D), C-contiguous) are written in place when given, as the reference writes into
+    the caller's pinned buffers (lib.rs:613-624)."""
     k = _c(keys_u16, np.uint16)
     v = None if vals_u16 is None else _c(vals_u16, np.uint16)
     q = _c(q_mean_u16, np.uint16)
     n_prob, n_max, dim = k.shape
     n = n_max if n is None else n
     ef_c = min(ef, n)
-    ok = np.zeros((n_prob, ef_c, dim), np.uint16) if gather else None
-    ov = np.zeros((n_prob, ef_c, dim), np.uint16) if (gather and v is not None) else None
+    for o in (out_keys, out_vals):
+        assert o is None or (o.dtype == np.uint16 and o.shape == (n_prob, ef_c, dim) and o.flags["C_CONTIGUOUS"])
+    ok = (out_keys if out_keys is not None else np.zeros((n_prob, ef_c, dim), np.uint16)) if gather else None
+    ov = (out_vals if out_vals is not None else np.zeros((n_prob, ef_c, dim), np.uint16)) if (gather and v is not None) else None
     oi = np.zeros((n_prob, ef_c), np.uint32)
     ob = np.zeros((n_prob, ef_c), np.uint32)
     got = lib().dco_query(_p(k), _p(v), n_max * dim, n_prob, n, dim, dtype, _p(q), ef, int(exact), n_threads,

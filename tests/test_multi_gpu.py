@@ -42,11 +42,28 @@ def _rank_main(rank, world, port, tmpdir):
             res_k[:, :, :rows] = k[:, :, lo:hi].cuda(); res_v[:, :, :rows] = v[:, :, lo:hi].cuda()
             if rank == world - 1:
                 kn, vn = k[:, :, -1].contiguous().cuda(), v[:, :, -1].contiguous().cuda()
-        step = sharded.SequenceShardedStep(sharded.GpuShardBackend(eng, start, res_k, res_v, rows, kn, vn), topk)
+        backend = sharded.GpuShardBackend(eng, start, res_k, res_v, rows, kn, vn)
+        step = sharded.SequenceShardedStep(backend, topk)     # NCCL all-gathers
         fast = step.step(q).clone()                          # keys-only exchange, prefix counts
         out = step.step(q, want_selection=True).clone()      # also ids + the full merge select
         sel = step.last_selection.clone()
         assert torch.equal(fast, out)
+        # the same step with both exchanges done by the step's own kernels over NVLink peer stores
+        peer_step = sharded.SequenceShardedStep(backend, topk, exchange="peer")
+        for _ in range(3):   # later rounds find the earlier rounds' blocks and epochs in the buffers
+            assert torch.equal(peer_step.step(q), fast)
+        g = torch.cuda.CUDAGraph()   # ... and replayed from a CUDA graph
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side), torch.cuda.graph(g, stream=side):
+            captured = peer_step.step(q)
+        torch.cuda.current_stream().wait_stream(side)
+        dist.barrier()
+        for _ in range(3):
+            g.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(captured, fast)
+        peer_step.xchg.check()
         eng.check_status()
         torch.cuda.synchronize()
         if rank == 0:  # single-GPU fused step on the whole sequence
@@ -84,12 +101,19 @@ def _stack_rank_main(rank, world, port, tmpdir):
     try:
         kw = dict(n_layers=3, hidden=512, batch=2, q_heads=16, kv_heads=4, head_dim=128, context=6000, topk=512, sink=16,
                   window=48, dtype="bf16", seed=77, device=torch.device("cuda", rank))
-        sharded_stack = AttentionStack(**kw)                       # kv heads split over the two ranks
+        sharded_stack = AttentionStack(**kw)                       # kv heads split over the two ranks, NCCL all-gather
         x = torch.randn((2, 512), generator=torch.Generator().manual_seed(3)).to(torch.bfloat16).cuda()
         y = sharded_stack.step(x).clone()
         for e in sharded_stack.engines:
             e.check_status()
         torch.cuda.synchronize()
+        peer_stack = AttentionStack(exchange="peer", **kw)         # the all-gather done by peer stores instead
+        assert peer_stack.exchange == "peer"
+        for _ in range(2):
+            assert torch.equal(peer_stack.step(x), y)
+        peer_stack.xchg.check()
+        dist.barrier()
+        peer_stack.close()
         if rank == 0:  # the same stack on one GPU: world of one
             solo = AttentionStack(unsharded=True, **kw)
             want = solo.step(x)

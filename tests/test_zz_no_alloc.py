@@ -38,7 +38,18 @@ def _attend(lib, pr, noalloc: bool):
             pr["sel"].data_ptr(), pr["n_sel"], pr["n_sel"], 0, pr["k_new"].data_ptr(), pr["v_new"].data_ptr(),
             rk.data_ptr(), rv.data_ptr(), sb, sh, pr["res_len"], 0.0, out.data_ptr(), lse.data_ptr(), None, None)
     if noalloc:
-        rc = lib.dc_sparse_attend_noalloc(*head, st)
+        # what the name promises: device memory in use is the same after the call as before it.  The
+        # scratch variant ran first, so the kernels are already loaded; nothing between the two readings
+        # allocates through torch.  (Repeated so that a one-off change made by something else on the
+        # device cannot fail the test.)
+        for attempt in range(3):
+            free_before = torch.cuda.mem_get_info()[0]
+            rc = lib.dc_sparse_attend_noalloc(*head, st)
+            torch.cuda.synchronize()
+            free_after = torch.cuda.mem_get_info()[0]
+            if rc != 0 or free_after >= free_before:
+                break
+        assert rc != 0 or free_after >= free_before, f"free device memory fell from {free_before} to {free_after}"
     else:
         scratch = torch.zeros(int(lib.dc_attend_scratch_bytes(P, G, D)), dtype=torch.uint8, device="cuda")
         rc = lib.dc_sparse_attend(*head, scratch.data_ptr(), st)

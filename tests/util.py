@@ -72,6 +72,26 @@ def oracle_decode_step(oracle, k_store, v_store, q_heads, group, topk, res_k, re
     return dict(idx=res["idx"], bits=res["bits"], all_bits=all_bits, out_f32=of, out_elem=oe, lse=lse, q_mean=q_mean)
 
 
+def oracle_attention_over(oracle, k_store, v_store, sel_idx, q_heads, group, res_k, res_v, k_new, v_new, scale, dtype):
+    """Oracle attention over the store rows `sel_idx` (P, k) — whatever rows were selected, e.g. the GPU's
+    own choice when it differs from the oracle's by an allowed boundary tie — plus the resident rows and
+    the new token.  Attention does not depend on the order of the rows.  Returns (out_f32, lse)."""
+    P = k_store.shape[0]
+    idx = np.asarray(sel_idx, dtype=np.int64).reshape(P, -1)
+    parts_k, parts_v = [], []
+    if idx.shape[1] > 0:
+        parts_k.append(np.stack([k_store[p][idx[p]] for p in range(P)]))
+        parts_v.append(np.stack([v_store[p][idx[p]] for p in range(P)]))
+    if res_k is not None and res_k.shape[1] > 0:
+        parts_k.append(res_k); parts_v.append(res_v)
+    if k_new is not None:
+        parts_k.append(k_new[:, None, :]); parts_v.append(v_new[:, None, :])
+    kk = np.ascontiguousarray(np.concatenate(parts_k, axis=1))
+    vv = np.ascontiguousarray(np.concatenate(parts_v, axis=1))
+    of, _, lse = oracle.attend(kk, vv, q_heads, group, scale, dtype)
+    return of, lse
+
+
 def small_problem(batch, kv_heads, group, n, head_dim, seed, dtype="bf16", device="cpu"):
     k, v = synth.make_kv(batch, kv_heads, n, head_dim, seed, dtype, device=device)
     q = synth.make_query(k, group, seed) if n > 0 else torch.randn(batch, kv_heads * group, head_dim).to(k.dtype)

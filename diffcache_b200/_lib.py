@@ -49,11 +49,10 @@ SIGNATURES = {
     "dc_xchg_open_peer": (_i32, [_vp, _i32, _vp]),
     "dc_xchg_set_peer": (_i32, [_vp, _i32, _vp]),
     "dc_xchg_local": (_vp, [_vp]),
-    "dc_xchg_channel": (_vp, [_vp, _i32]),
     "dc_xchg_set_timeout_ms": (_i32, [_vp, _i32]),
     "dc_xchg_push": (_i32, [_vp, _i32, _vp, _i64, _u64]),
     "dc_xchg_push_rows": (_i32, [_vp, _i32, _vp, _i64, _i64, _u64]),
-    "dc_xchg_wait": (_i32, [_vp, _i32, _u64]),
+    "dc_xchg_collect": (_i32, [_vp, _i32, _vp, _i64, _u64]),
     "dc_xchg_check": (_i32, [_vp, _u64]),
     "dc_sharded_slot_bytes": (_i32, [_vp, _i32, _vp]),
     "dc_sharded_local": (_i32, [_vp, _vp, _vp, _i32, _u64]),

@@ -435,10 +435,9 @@ __global__ void __launch_bounds__(kCombineThreads)
 lse_combine_kernel(const float* __restrict__ part_acc, int64_t acc_ps, int64_t acc_rs,
                    const float* __restrict__ part_ml, int64_t ml_ps, int64_t ml_rs, int n_part, int dim,
                    uint16_t* __restrict__ out, float* __restrict__ out_lse, float* __restrict__ out_acc,
-                   float* __restrict__ out_ml, const XchgWait wait) {
+                   float* __restrict__ out_ml, const XchgLL ll, int64_t ll_ml_off) {
     pdl_launch_dependents();
     pdl_wait();
-    xchg_wait_all(wait);   // parts delivered by peer stores: wait until every rank's has arrived (no-op otherwise)
     const int64_t row = blockIdx.x;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     __shared__ float s_w[kCombineMaxParts];   // weight of every part: exp2(m_s - M)
@@ -446,6 +445,28 @@ lse_combine_kernel(const float* __restrict__ part_acc, int64_t acc_ps, int64_t a
     __shared__ float s_M, s_L;
     const float* ml = part_ml + row * ml_rs;
     const float* acc = part_acc + row * acc_rs;
+    // Parts delivered by peer stores as {word, epoch} pairs into this rank's exchange buffer (slot s = part s,
+    // holding [acc (rows, dim) | ml (rows, 2)]): this row's words are polled until they carry the current epoch
+    // and staged in shared memory, which then takes the place of the global arrays.
+    __shared__ __align__(16) float s_stage[kXchgMaxWorld * (256 + 4)];
+    if (ll.chan != nullptr) {
+        const int row_stride = dim + 4;   // dim accumulators, (m, l), padding that keeps rows 16-byte aligned
+        const uint32_t want = ll.epoch[ll.channel];
+        const unsigned long long t0 = global_timer_ns();
+        bool fail = false;
+        const int per = dim / 2 + 1;      // pair vectors per part: dim / 2 of accumulators, one of (m, l)
+        for (int i = tid; i < n_part * per; i += kCombineThreads) {
+            const int s = i / per, v = i % per;
+            const int64_t word = v < dim / 2 ? row * dim + 2 * v : ll_ml_off + row * 2;
+            const uint2 d = xchg_poll(ll.chan + s * ll.slot_vecs + word / 2, want, ll, t0, fail);
+            float* dst = s_stage + s * row_stride + (v < dim / 2 ? 2 * v : dim);
+            dst[0] = __uint_as_float(d.x);
+            dst[1] = __uint_as_float(d.y);
+        }
+        __syncthreads();
+        acc = s_stage; acc_ps = row_stride;
+        ml = s_stage + dim; ml_ps = row_stride;
+    }
     // M = max_s m_s
     float m = -INFINITY;
     for (int s = tid; s < n_part; s += kCombineThreads) m = fmaxf(m, ml[s * ml_ps]);
@@ -481,7 +502,7 @@ lse_combine_kernel(const float* __restrict__ part_acc, int64_t acc_ps, int64_t a
     __syncthreads();
     const float L = s_L;
     const bool vec_ok = (dim % 4 == 0) && (dim / 4 <= kCombineThreads) && (kCombineThreads % (dim / 4) == 0) &&
-                        (acc_ps % 4 == 0) && (acc_rs % 4 == 0) && ((reinterpret_cast<uintptr_t>(part_acc) & 15) == 0);
+                        (acc_ps % 4 == 0) && ((reinterpret_cast<uintptr_t>(acc) & 15) == 0);
     if (vec_ok) {
         // 16-byte loads; the parts are dealt round-robin to dim/4-lane groups so that their loads are
         // in flight together, and the groups' sums are added through shared memory
@@ -563,20 +584,24 @@ int64_t attend_scratch_bytes(int n_prob, int group, int head_dim) {
 
 int lse_combine(const float* acc, int64_t acc_ps, int64_t acc_rs, const float* ml, int64_t ml_ps, int64_t ml_rs,
                 int n_part, int64_t rows, int head_dim, int dtype, void* out, float* out_lse, float* out_acc,
-                float* out_ml, cudaStream_t stream, const XchgWait* wait) {
-    DC_REQUIRE(acc && ml && n_part >= 1 && rows >= 0, "lse_combine: bad arguments");
+                float* out_ml, cudaStream_t stream, const XchgLL* ll) {
+    // ll (may be NULL): the parts arrive in pair format in an exchange channel instead of acc / ml
+    DC_REQUIRE(((acc && ml) || ll) && n_part >= 1 && rows >= 0, "lse_combine: bad arguments");
+    DC_REQUIRE(ll == nullptr || (n_part <= kXchgMaxWorld && head_dim <= 256 && head_dim % 2 == 0),
+               "lse_combine: parts from the peer exchange: at most %d parts, even head_dim <= 256", kXchgMaxWorld);
     DC_REQUIRE(dtype == DC_BF16 || dtype == DC_FP16, "lse_combine: dtype %d not supported", dtype);
     DC_REQUIRE(n_part <= kCombineMaxParts, "lse_combine: n_part=%d exceeds %d", n_part, kCombineMaxParts);
     if (rows == 0) return DC_OK;
     const dim3 grid(static_cast<unsigned>(rows)), block(kCombineThreads);
-    XchgWait w = {};
-    if (wait != nullptr) w = *wait;
+    XchgLL w = {};
+    if (ll != nullptr) w = *ll;
+    const int64_t ml_off = rows * head_dim;   // word offset of the (m, l) block inside a part's slot
     if (dtype == DC_BF16)
         DC_CUDA_TRY(launch_chained(lse_combine_kernel<DC_BF16>, grid, block, 0, stream, 0u, acc, acc_ps, acc_rs, ml, ml_ps,
-                                   ml_rs, n_part, head_dim, static_cast<uint16_t*>(out), out_lse, out_acc, out_ml, w));
+                                   ml_rs, n_part, head_dim, static_cast<uint16_t*>(out), out_lse, out_acc, out_ml, w, ml_off));
     else
         DC_CUDA_TRY(launch_chained(lse_combine_kernel<DC_FP16>, grid, block, 0, stream, 0u, acc, acc_ps, acc_rs, ml, ml_ps,
-                                   ml_rs, n_part, head_dim, static_cast<uint16_t*>(out), out_lse, out_acc, out_ml, w));
+                                   ml_rs, n_part, head_dim, static_cast<uint16_t*>(out), out_lse, out_acc, out_ml, w, ml_off));
     return DC_OK;
 }
 

@@ -26,7 +26,7 @@ int topk_select(const uint32_t* bits, const uint32_t* ids, int64_t in_stride, in
 int select_prepare();
 int64_t select_scratch_bytes(int n_prob);
 int merge_sorted_count(const uint32_t* bits_all, int world, int n_prob, int k, int my_rank, int32_t* out_count,
-                       cudaStream_t stream, const XchgWait* wait = nullptr, int64_t rank_stride = 0);
+                       cudaStream_t stream, const XchgLL* ll = nullptr, int64_t rank_stride = 0);
 int sparse_attend(const void* k_store, const void* v_store, int64_t prob_stride, int64_t n_rows, int n_prob,
                   int kv_heads, int group, int head_dim, int dtype, const void* q, const uint32_t* sel,
                   int64_t sel_stride, int n_sel, int64_t sel_base, const void* k_new, const void* v_new, void* res_k,
@@ -39,7 +39,7 @@ int adaptive_budget(const uint32_t* bits, int64_t stride, int n_prob, int k, int
 int64_t attend_scratch_bytes(int n_prob, int group, int head_dim);
 int lse_combine(const float* acc, int64_t acc_ps, int64_t acc_rs, const float* ml, int64_t ml_ps, int64_t ml_rs,
                 int n_part, int64_t rows, int head_dim, int dtype, void* out, float* out_lse, float* out_acc,
-                float* out_ml, cudaStream_t stream, const XchgWait* wait = nullptr);
+                float* out_ml, cudaStream_t stream, const XchgLL* ll = nullptr);
 int pq_build_lut(const void* q, int q_mode, int group, int dtype, const float* centroids, int n_prob, int head_dim,
                  int n_sub, float* lut, cudaStream_t stream);
 int pq_adc_scan(const uint8_t* codes, int64_t prob_stride, int n_prob, int64_t n, int n_sub, const float* lut,
@@ -920,7 +920,8 @@ int dc_sharded_slot_bytes(dc_engine* e, int topk, int64_t* out2) {
 int dc_sharded_local(dc_engine* e, dc_xchg* x, const void* q, int topk, uint64_t stream) {
     DC_ENGINE_ENTER(e);
     DC_REQUIRE(x != nullptr && q != nullptr, "dc_sharded_local: null pointer");
-    DC_REQUIRE(topk >= 1 && topk <= DC_MAX_TOPK, "dc_sharded_local: topk=%d outside [1, %d]", topk, DC_MAX_TOPK);
+    DC_REQUIRE(topk >= 2 && topk <= DC_MAX_TOPK && topk % 2 == 0, "dc_sharded_local: topk=%d must be even, in [2, %d]", topk,
+               DC_MAX_TOPK);
     DC_REQUIRE(static_cast<int64_t>(xchg_world(x)) * topk * 4 <= 200 * 1024,
                "dc_sharded_local: world*topk=%lld keys do not fit the prefix-count kernel (200 KB of shared memory)",
                static_cast<long long>(xchg_world(x)) * topk);
@@ -956,9 +957,8 @@ int dc_sharded_attend(dc_engine* e, dc_xchg* x, const void* q, const void* k_new
     DC_REQUIRE(e->shard_k > 0, "dc_sharded_attend: dc_sharded_local has not run");
     cudaStream_t s = as_stream(stream);
     const int k = e->shard_k;
-    const XchgWait w0 = xchg_wait_args(x, 0);
-    int rc = merge_sorted_count(reinterpret_cast<const uint32_t*>(xchg_channel_data(x, 0)), xchg_world(x), e->n_prob, k,
-                                xchg_rank(x), e->shard_count, s, &w0, xchg_slot_bytes(x, 0) / 4);
+    const XchgLL w0 = xchg_ll_args(x, 0);
+    int rc = merge_sorted_count(nullptr, xchg_world(x), e->n_prob, k, xchg_rank(x), e->shard_count, s, &w0, 0);
     if (rc) return rc;
     trace_mark(e, s);
     const int64_t rows = static_cast<int64_t>(e->n_prob) * e->group;
@@ -975,11 +975,9 @@ int dc_sharded_combine(dc_engine* e, dc_xchg* x, void* out, float* out_lse, uint
     DC_ENGINE_ENTER(e);
     DC_REQUIRE(x != nullptr && out != nullptr, "dc_sharded_combine: null pointer");
     const int64_t rows = static_cast<int64_t>(e->n_prob) * e->group;
-    const float* parts = reinterpret_cast<const float*>(xchg_channel_data(x, 1));
-    const int64_t stride = xchg_slot_bytes(x, 1) / 4;
-    const XchgWait w1 = xchg_wait_args(x, 1);
-    int rc = lse_combine(parts, stride, e->head_dim, parts + rows * e->head_dim, stride, 2, xchg_world(x), rows,
-                         e->head_dim, e->dtype, out, out_lse, nullptr, nullptr, as_stream(stream), &w1);
+    const XchgLL w1 = xchg_ll_args(x, 1);
+    int rc = lse_combine(nullptr, 0, 0, nullptr, 0, 0, xchg_world(x), rows, e->head_dim, e->dtype, out, out_lse, nullptr,
+                         nullptr, as_stream(stream), &w1);
     if (rc) return rc;
     return trace_mark(e, as_stream(stream));
 }

@@ -4,20 +4,19 @@
 // attention results).  Through a collective library each exchange costs a launch plus a protocol round
 // trip; here every rank owns one buffer that all its peers have mapped (CUDA IPC), a producer kernel
 // stores its block straight into slot `rank` of EVERY peer's buffer with plain 16-byte st.global over
-// NVLink, and then raises a flag word in each peer's buffer; the consumer kernel (prefix count, partial
-// merge) polls the flags of its own buffer in its prologue and then reads only local memory.  No K/V row,
+// NVLink, and the consumer kernel (prefix count, partial merge) reads only its own buffer.  No K/V row,
 // and no load, ever crosses NVLink; there is no multicast and no library kernel on peer memory.
 //
-// Ordering.  Producer: data stores -> fence.sys by every thread -> block barrier -> a counter tells which
-// CTA finished last -> that CTA release-stores the flags (value = the epoch of this exchange) at system
-// scope.  Consumer: acquire-loads at system scope until every flag holds the epoch, then a block barrier.
-// Epochs only grow, so flags are never reset.  One buffer per channel suffices: a rank can only start
-// the next step's exchange on a channel after it consumed every peer's block of the other channel of the
-// current step, which every peer sent after it finished reading this channel.
+// Arrival is signalled by the data itself: every 32-bit word is stored as an 8-byte pair {word, epoch}
+// (exchange.cuh), an aligned 8-byte store is indivisible, so the consumer polls the pairs it needs until they
+// carry the epoch of the current exchange.  No fence, no flag word, no extra round trip.  Epochs only grow.
+// One buffer per channel suffices for the sharded step: a rank can only start the next step's exchange on a
+// channel after it consumed every peer's block of the other channel of the current step, which every peer
+// sent after it finished reading this channel.  (A user with ONE exchange per step alternates channels.)
 //
 // Every wait is bounded (wall-clock limit, default 2 s): when it runs out the kernel records status
-// 401 + channel, stops waiting and finishes on whatever the buffer holds, so a missing peer shows up as an
-// error status on the host (dc_xchg_check), never as a hung GPU.
+// 401 + channel, stops waiting and finishes on zeros, so a missing peer shows up as an error status on the
+// host (dc_xchg_check), never as a hung GPU.
 //
 // The reference has no counterpart (single process, single GPU: src/diffcache/base.py:28).
 #include <cstdlib>
@@ -31,46 +30,53 @@ namespace {
 
 constexpr int kPushThreads = 256;
 
-__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;\n" ::"l"(p), "r"(v) : "memory");
+__device__ __forceinline__ void st_pairs16(uint4* p, uint32_t a, uint32_t b, uint32_t epoch) {
+    asm volatile("st.volatile.global.v4.u32 [%0], {%1,%2,%3,%4};\n" ::"l"(p), "r"(a), "r"(epoch), "r"(b), "r"(epoch) : "memory");
 }
 
-// grid = (n_cta); copies n_vec 16-byte vectors from src into every peer's channel, then the last CTA to
-// finish publishes the new epoch in every peer's flag word for (channel, rank).  The source is
-// (rows, vec_per_row) dense; vector (row, col) lands at vector index row * row_stride + rank_off + col of the
-// channel: one block per rank (rows = 1, rank_off = rank * slot) or rows interleaved by rank
-// (row_stride = world * vec_per_row, rank_off = rank * vec_per_row).
+// grid = (n_cta); sends n_vec 16-byte source vectors (4 words each -> two 16-byte pair vectors) into every
+// peer's channel, tagged with the next epoch of the channel.  The source is (rows, vec_per_row) dense; source
+// vector (row, col) lands at source-vector index row * row_stride + rank_off + col of the channel: one block
+// per rank (rows = 1, rank_off = rank * slot) or rows interleaved by rank (row_stride = world * vec_per_row,
+// rank_off = rank * vec_per_row).  The CTA that finishes last advances the channel's epoch word, which
+// later kernels of this rank's stream read.
 __global__ void __launch_bounds__(kPushThreads)
 xchg_push_kernel(const uint4* __restrict__ src, int64_t n_vec, int64_t vec_per_row, int64_t row_stride, int64_t rank_off,
-                 XchgPeers peers, int64_t chan_off, int channel, int rank, int world, uint32_t* epoch, uint32_t* done) {
+                 XchgPeers peers, int64_t chan_off, int channel, int world, uint32_t* epoch, uint32_t* done) {
     pdl_launch_dependents();
     pdl_wait();
     const uint32_t next = epoch[channel] + 1u;   // every CTA reads it before the last one can have bumped it
     const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
     for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n_vec; i += stride) {
         const uint4 w = src[i];
-        const int64_t at = (i / vec_per_row) * row_stride + rank_off + (i % vec_per_row);
-        for (int r = 0; r < world; r++) reinterpret_cast<uint4*>(peers.base[r] + chan_off)[at] = w;
+        const int64_t at = 2 * ((i / vec_per_row) * row_stride + rank_off + (i % vec_per_row));
+        for (int r = 0; r < world; r++) {
+            uint4* dst = reinterpret_cast<uint4*>(peers.base[r] + chan_off) + at;
+            st_pairs16(dst, w.x, w.y, next);
+            st_pairs16(dst + 1, w.z, w.w, next);
+        }
     }
-    __threadfence_system();
     __syncthreads();
-    __shared__ bool s_last;
-    if (threadIdx.x == 0) s_last = atomicAdd(done, 1u) == gridDim.x - 1;
-    __syncthreads();
-    if (!s_last) return;
-    __threadfence_system();
-    if (threadIdx.x < world)
-        st_release_sys(xchg_flag(peers.base[threadIdx.x], channel, rank), next);
-    if (threadIdx.x == 0) {
+    if (threadIdx.x == 0 && atomicAdd(done, 1u) == gridDim.x - 1) {
         *done = 0u;
         epoch[channel] = next;
     }
 }
 
-__global__ void xchg_wait_kernel(XchgWait w) {
+// Waits for the blocks of all ranks in this rank's copy of a channel and writes their payload densely to dst
+// (world * slot words): for consumers that are not kernels of this library.
+__global__ void __launch_bounds__(256)
+xchg_collect_kernel(XchgLL w, uint32_t* __restrict__ dst, int64_t n_vec_total) {
     pdl_launch_dependents();
     pdl_wait();
-    xchg_wait_all(w);
+    const uint32_t want = w.epoch[w.channel];
+    const unsigned long long t0 = global_timer_ns();
+    bool fail = false;
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n_vec_total; i += stride) {
+        const uint2 v = xchg_poll(w.chan + i, want, w, t0, fail);
+        reinterpret_cast<uint2*>(dst)[i] = v;
+    }
 }
 
 }  // namespace
@@ -80,12 +86,12 @@ using namespace dc;
 
 struct dc_xchg {
     int rank = 0, world = 1, device = 0, n_channels = 0;
-    unsigned char* local = nullptr;            // this rank's buffer: flags, then the channels
+    unsigned char* local = nullptr;            // this rank's buffer: the channels, in pair format
     size_t bytes = 0;
     unsigned char* peer[kXchgMaxWorld] = {};   // base of every rank's buffer as mapped here (peer[rank] == local)
     bool opened[kXchgMaxWorld] = {};           // mapped with cudaIpcOpenMemHandle (to be closed)
     int64_t chan_off[kXchgChannels] = {};      // byte offset of each channel's data
-    int64_t slot_bytes[kXchgChannels] = {};    // bytes per rank in each channel
+    int64_t slot_bytes[kXchgChannels] = {};    // PAYLOAD bytes per rank in each channel (the buffer holds twice that)
     uint32_t* words = nullptr;                 // device: epoch[kXchgChannels], done counter, status
     unsigned long long timeout_ns = 2000ull * 1000 * 1000;
 };
@@ -117,9 +123,10 @@ XchgPeers peers_of(const dc_xchg* x) {
 
 namespace dc {
 
-XchgWait xchg_wait_args(const dc_xchg* x, int channel) {
-    XchgWait w;
-    w.flags = reinterpret_cast<const uint32_t*>(x->local);
+XchgLL xchg_ll_args(const dc_xchg* x, int channel) {
+    XchgLL w;
+    w.chan = reinterpret_cast<const uint4*>(x->local + x->chan_off[channel]);
+    w.slot_vecs = x->slot_bytes[channel] / 8;
     w.epoch = x->words;
     w.status = x->words + kXchgChannels + 1;
     w.channel = channel;
@@ -128,7 +135,6 @@ XchgWait xchg_wait_args(const dc_xchg* x, int channel) {
     return w;
 }
 
-const unsigned char* xchg_channel_data(const dc_xchg* x, int channel) { return x->local + x->chan_off[channel]; }
 int xchg_world(const dc_xchg* x) { return x->world; }
 int xchg_rank(const dc_xchg* x) { return x->rank; }
 int64_t xchg_slot_bytes(const dc_xchg* x, int channel) { return x->slot_bytes[channel]; }
@@ -153,7 +159,7 @@ int dc_xchg_create(int rank, int world, int device, const int64_t* slot_bytes, i
     if (!guard.ok) { set_error("dc_xchg_create: cannot select device %d", device); return DC_ECUDA; }
     dc_xchg* x = new dc_xchg();
     x->rank = rank; x->world = world; x->device = device; x->n_channels = n_channels;
-    size_t off = kXchgFlagBytes;
+    size_t off = 0;
     for (int c = 0; c < n_channels; c++) {
         if (slot_bytes[c] < 0 || slot_bytes[c] % 16 != 0) {
             delete x;
@@ -163,9 +169,9 @@ int dc_xchg_create(int rank, int world, int device, const int64_t* slot_bytes, i
         }
         x->chan_off[c] = static_cast<int64_t>(off);
         x->slot_bytes[c] = slot_bytes[c];
-        off += (static_cast<size_t>(slot_bytes[c]) * world + 255) / 256 * 256;
+        off += (2 * static_cast<size_t>(slot_bytes[c]) * world + 255) / 256 * 256;   // pairs: twice the payload
     }
-    x->bytes = off;
+    x->bytes = std::max<size_t>(off, 256);
     cudaError_t err = cudaMalloc(reinterpret_cast<void**>(&x->local), x->bytes);
     if (err == cudaSuccess) err = cudaMemset(x->local, 0, x->bytes);
     if (err == cudaSuccess) err = cudaMalloc(reinterpret_cast<void**>(&x->words), 256);
@@ -233,11 +239,6 @@ int dc_xchg_set_peer(dc_xchg* x, int peer_rank, void* base) {
 
 void* dc_xchg_local(dc_xchg* x) { return x ? x->local : nullptr; }
 
-void* dc_xchg_channel(dc_xchg* x, int channel) {
-    if (x == nullptr || channel < 0 || channel >= x->n_channels) return nullptr;
-    return x->local + x->chan_off[channel];
-}
-
 int dc_xchg_set_timeout_ms(dc_xchg* x, int ms) {
     DC_REQUIRE(x != nullptr && ms >= 1, "dc_xchg_set_timeout_ms: bad arguments");
     x->timeout_ns = static_cast<unsigned long long>(ms) * 1000ull * 1000ull;
@@ -246,11 +247,10 @@ int dc_xchg_set_timeout_ms(dc_xchg* x, int ms) {
 
 static int xchg_push_launch(dc_xchg* x, int channel, const void* src, int64_t n_vec, int64_t vec_per_row,
                             int64_t row_stride, int64_t rank_off, uint64_t stream) {
-    const int n_cta = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(32, (n_vec + kPushThreads * 4 - 1) / (kPushThreads * 4))));
+    const int n_cta = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(32, (n_vec + kPushThreads - 1) / kPushThreads)));
     DC_CUDA_TRY(launch_chained(xchg_push_kernel, dim3(n_cta), dim3(kPushThreads), 0, as_stream(stream), 0u,
                                static_cast<const uint4*>(src), n_vec, std::max<int64_t>(1, vec_per_row), row_stride, rank_off,
-                               peers_of(x), x->chan_off[channel], channel, x->rank, x->world, x->words,
-                               x->words + kXchgChannels));
+                               peers_of(x), x->chan_off[channel], channel, x->world, x->words, x->words + kXchgChannels));
     return DC_OK;
 }
 
@@ -279,10 +279,17 @@ int dc_xchg_push_rows(dc_xchg* x, int channel, const void* src, int64_t rows, in
                             static_cast<int64_t>(x->rank) * vpr, stream);
 }
 
-int dc_xchg_wait(dc_xchg* x, int channel, uint64_t stream) {
+int dc_xchg_collect(dc_xchg* x, int channel, void* dst, int64_t bytes, uint64_t stream) {
     DC_XCHG_ENTER(x);
-    DC_REQUIRE(channel >= 0 && channel < x->n_channels, "dc_xchg_wait: channel %d", channel);
-    DC_CUDA_TRY(launch_chained(xchg_wait_kernel, dim3(1), dim3(32), 0, as_stream(stream), 0u, xchg_wait_args(x, channel)));
+    DC_REQUIRE(channel >= 0 && channel < x->n_channels, "dc_xchg_collect: channel %d", channel);
+    DC_REQUIRE(dst != nullptr && bytes >= 0 && bytes % 8 == 0 && bytes <= x->slot_bytes[channel] * x->world &&
+                   (reinterpret_cast<uintptr_t>(dst) & 7) == 0,
+               "dc_xchg_collect: %lld bytes exceed the channel's %lld (8-byte multiples, 8-byte aligned destination)",
+               static_cast<long long>(bytes), static_cast<long long>(x->slot_bytes[channel] * x->world));
+    const int64_t n_vec = bytes / 8;   // one 16-byte pair vector per 8 payload bytes
+    const int n_cta = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(32, (n_vec + 255) / 256)));
+    DC_CUDA_TRY(launch_chained(xchg_collect_kernel, dim3(n_cta), dim3(256), 0, as_stream(stream), 0u, xchg_ll_args(x, channel),
+                               static_cast<uint32_t*>(dst), n_vec));
     return DC_OK;
 }
 

@@ -10,32 +10,30 @@ namespace dc {
 
 constexpr int kXchgMaxWorld = 16;
 constexpr int kXchgChannels = 4;
-constexpr int kXchgFlagStride = 128;   // bytes between two flag words (one cache line each)
-constexpr size_t kXchgFlagBytes = static_cast<size_t>(kXchgChannels) * kXchgMaxWorld * kXchgFlagStride;
 
-// Buffer of a rank: [flags: kXchgChannels x kXchgMaxWorld words, 128 bytes apart | channel 0 | channel 1 | ...];
-// channel c holds `world` slots of slot_bytes[c]; flag (c, r) = epoch of the last block of rank r that has
-// completely arrived in slot r of channel c of THIS buffer.
+// Wire format.  Every 32-bit payload word travels as an 8-byte pair {word, epoch}: an aligned 8-byte store is
+// indivisible, so a reader that sees the epoch it expects also sees the word that came with it — the data
+// carries its own "arrived" flag and needs neither a fence nor a separate flag round trip.  Two pairs are
+// moved per 16-byte access.  A channel of a rank's buffer holds `world` slots of slot_words pairs each;
+// slot r is written by rank r (into EVERY rank's buffer) and read only by the buffer's owner.
 struct XchgPeers {
     unsigned char* base[kXchgMaxWorld];
 };
 
-__host__ __device__ __forceinline__ uint32_t* xchg_flag(unsigned char* base, int channel, int rank) {
-    return reinterpret_cast<uint32_t*>(base + (static_cast<size_t>(channel) * kXchgMaxWorld + rank) * kXchgFlagStride);
-}
-
-struct XchgWait {
-    const uint32_t* flags;        // this rank's buffer (its flag region comes first); nullptr = nothing to wait for
+// What a consumer needs to read one channel of its own buffer.
+struct XchgLL {
+    const uint4* chan;            // this rank's copy of the channel (nullptr: the kernel reads plain memory instead)
+    int64_t slot_vecs;            // 16-byte vectors (2 pairs) per rank slot
     const uint32_t* epoch;        // this rank's epoch words: epoch[channel] = exchanges started on the channel
-    uint32_t* status;             // receives 401 + channel when the wait runs out
+    uint32_t* status;             // receives 401 + channel when a wait runs out
     int channel;
     int world;
     unsigned long long timeout_ns;
 };
 
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
-    uint32_t v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];\n" : "=r"(v) : "l"(p) : "memory");
+__device__ __forceinline__ uint4 ld_volatile16(const uint4* p) {
+    uint4 v;
+    asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
     return v;
 }
 
@@ -45,31 +43,27 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
     return t;
 }
 
-// Block-wide: returns when every rank's block of the current epoch has arrived in this rank's buffer, or
-// when the time limit (and, as a second bound, an iteration limit) runs out, in which case the status word
-// is set and the caller goes on with whatever the buffer holds.  Call from all threads of the block, after
-// pdl_wait(); blockDim.x >= world.
-__device__ __forceinline__ void xchg_wait_all(const XchgWait& w) {
-    if (w.flags != nullptr) {
-        if (static_cast<int>(threadIdx.x) < w.world) {
-            const uint32_t want = w.epoch[w.channel];
-            const uint32_t* f = w.flags + (static_cast<size_t>(w.channel) * kXchgMaxWorld + threadIdx.x) * (kXchgFlagStride / 4);
-            const unsigned long long t0 = global_timer_ns();
-            bool ok = false;
-            for (unsigned it = 0; it < (1u << 27); it++) {
-                if (static_cast<int32_t>(ld_acquire_sys(f) - want) >= 0) { ok = true; break; }
+// Two payload words of vector `p` once both carry epoch `want`.  Bounded: when the time limit (or, as a second
+// bound, the iteration limit) runs out, the status word is set, `fail` becomes true and zeros come back, so the
+// caller finishes on harmless data and the host learns of the missing peer from the status.
+__device__ __forceinline__ uint2 xchg_poll(const uint4* p, uint32_t want, const XchgLL& w, unsigned long long t0, bool& fail) {
+    if (!fail) {
+        for (unsigned it = 0; it < (1u << 26); it++) {
+            const uint4 v = ld_volatile16(p);
+            if (v.y == want && v.w == want) return make_uint2(v.x, v.z);
+            if ((it & 15u) == 15u) {
                 if (global_timer_ns() - t0 > w.timeout_ns) break;
-                __nanosleep(40);
+                __nanosleep(20);
             }
-            if (!ok) atomicMax(w.status, 401u + static_cast<uint32_t>(w.channel));
         }
-        __syncthreads();
+        fail = true;
+        atomicMax(w.status, 401u + static_cast<uint32_t>(w.channel));
     }
+    return make_uint2(0u, 0u);
 }
 
 // host-side accessors used by the engine's sharded step
-XchgWait xchg_wait_args(const dc_xchg* x, int channel);
-const unsigned char* xchg_channel_data(const dc_xchg* x, int channel);
+XchgLL xchg_ll_args(const dc_xchg* x, int channel);
 int xchg_world(const dc_xchg* x);
 int xchg_rank(const dc_xchg* x);
 int64_t xchg_slot_bytes(const dc_xchg* x, int channel);

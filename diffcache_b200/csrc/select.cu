@@ -456,8 +456,8 @@ topk_select_kernel(const uint32_t* __restrict__ bits, const uint32_t* __restrict
         // Winners are ~k of n scores, so a 32-bit pre-test on the dist bits rejects almost every
         // element before its id is looked at; positions come from one shared-memory atomic each.
         const uint32_t hi32 = static_cast<uint32_t>(hi >> 32);
-        auto place = [&](uint32_t b, uint32_t i) {
-            const unsigned long long key = key_of(b, i);
+        auto place_key = [&](unsigned long long key) {
+            const uint32_t b = static_cast<uint32_t>(key >> 32);
             if (key < lo) {
                 uint32_t pos;
                 if (bucket) {
@@ -478,13 +478,36 @@ topk_select_kernel(const uint32_t* __restrict__ bits, const uint32_t* __restrict
                 }
             }
         };
+        auto place = [&](uint32_t b, uint32_t i) { place_key(key_of(b, i)); };
+        bool placed = false;
         if (listed) {  // every key up to the threshold bin is already in shared memory
             const uint32_t extent = ctl.raw_count;
             for (uint32_t r = tid; r < extent; r += kSelThreads) {
                 const unsigned long long e = s_raw[r];
                 if (e != ~0ull) place(static_cast<uint32_t>(e >> 32), static_cast<uint32_t>(e & 0xFFFFFFFFull));
             }
-        } else {
+            placed = true;
+        } else if (csize > 1 && raw_cap > 0) {
+            // Cluster: placing straight from the scan makes every thread walk a serial chain of remote
+            // shared-memory round trips (one per winner it happens to hold).  Instead the CTA first gathers its
+            // winners and threshold-bin keys in its OWN shared memory (local atomics), then all threads flush
+            // that short list together, about one entry each, so the remote round trips overlap.
+            for_each_score(pb, begin, end, [&](uint32_t b, uint32_t i) {
+                if (b > hi32) return;
+                const unsigned long long key = key_of(b, i);
+                if (key <= hi) {
+                    const uint32_t pos = atomicAdd(&ctl.raw_count, 1u);
+                    if (pos < static_cast<uint32_t>(raw_cap)) s_raw[pos] = key;
+                }
+            });
+            __syncthreads();
+            const uint32_t cnt = ctl.raw_count;
+            if (cnt <= static_cast<uint32_t>(raw_cap)) {   // (a slice with more keys than fit is placed directly below)
+                for (uint32_t r = tid; r < cnt; r += kSelThreads) place_key(s_raw[r]);
+                placed = true;
+            }
+        }
+        if (!placed) {
             for_each_score(pb, begin, end, [&](uint32_t b, uint32_t i) {
                 if (b > hi32) return;
                 place(b, i);
@@ -567,13 +590,28 @@ constexpr int kMergeThreads = 1024;
 
 __global__ void __launch_bounds__(kMergeThreads)
 merge_sorted_count_kernel(const uint32_t* __restrict__ bits_all, int64_t rank_stride, int world, int n_prob, int k,
-                          int my_rank, int32_t* __restrict__ out_count, const XchgWait wait) {
+                          int my_rank, int32_t* __restrict__ out_count, const XchgLL ll) {
     pdl_launch_dependents();
     pdl_wait();
-    xchg_wait_all(wait);   // lists delivered by peer stores: wait until every rank's has arrived (no-op otherwise)
     extern __shared__ __align__(16) uint32_t s_lists[];
     __shared__ int s_sum[kMergeThreads / 32];
     const int p = blockIdx.x, tid = threadIdx.x;
+    if (ll.chan != nullptr) {
+        // lists delivered by peer stores as {key, epoch} pairs into this rank's exchange buffer: every pair is
+        // polled until it carries the current epoch (k is even, so a problem's list starts on a pair vector)
+        const uint32_t want = ll.epoch[ll.channel];
+        const unsigned long long t0 = global_timer_ns();
+        bool fail = false;
+        for (int r = 0; r < world; r++) {
+            const uint4* src = ll.chan + r * ll.slot_vecs + (static_cast<int64_t>(p) * k) / 2;
+            uint32_t* dst = s_lists + static_cast<size_t>(r) * k;
+            for (int v = tid; v < k / 2; v += kMergeThreads) {
+                const uint2 d = xchg_poll(src + v, want, ll, t0, fail);
+                dst[2 * v] = d.x;
+                dst[2 * v + 1] = d.y;
+            }
+        }
+    } else
     for (int r = 0; r < world; r++) {
         const uint32_t* src = bits_all + r * rank_stride + static_cast<int64_t>(p) * k;   // rank r's (n_prob, k) lists
         uint32_t* dst = s_lists + static_cast<size_t>(r) * k;
@@ -618,10 +656,12 @@ merge_sorted_count_kernel(const uint32_t* __restrict__ bits_all, int64_t rank_st
 }  // namespace
 
 // rank_stride: elements between two ranks' (n_prob, k) lists; 0 = dense (n_prob * k).
+// ll (may be NULL): the lists arrive in pair format in an exchange channel instead of bits_all.
 int merge_sorted_count(const uint32_t* bits_all, int world, int n_prob, int k, int my_rank, int32_t* out_count,
-                       cudaStream_t stream, const XchgWait* wait, int64_t rank_stride) {
+                       cudaStream_t stream, const XchgLL* ll, int64_t rank_stride) {
     if (rank_stride == 0) rank_stride = static_cast<int64_t>(n_prob) * k;
-    DC_REQUIRE(bits_all && out_count, "merge_sorted_count: null pointer");
+    DC_REQUIRE((bits_all || ll) && out_count, "merge_sorted_count: null pointer");
+    DC_REQUIRE(ll == nullptr || k % 2 == 0, "merge_sorted_count: k=%d must be even for lists delivered by the peer exchange", k);
     DC_REQUIRE(world >= 1 && my_rank >= 0 && my_rank < world, "merge_sorted_count: rank %d of %d", my_rank, world);
     DC_REQUIRE(k >= 1 && k <= DC_MAX_TOPK, "merge_sorted_count: k=%d outside [1, %d]", k, DC_MAX_TOPK);
     DC_REQUIRE(n_prob >= 0 && n_prob <= 65535, "merge_sorted_count: n_prob=%d", n_prob);
@@ -635,8 +675,8 @@ int merge_sorted_count(const uint32_t* bits_all, int world, int n_prob, int k, i
         return DC_OK;
     });
     if (rc0 != DC_OK) return rc0;
-    XchgWait w = {};
-    if (wait != nullptr) w = *wait;
+    XchgLL w = {};
+    if (ll != nullptr) w = *ll;
     DC_CUDA_TRY(launch_chained(merge_sorted_count_kernel, dim3(n_prob), dim3(kMergeThreads), smem, stream, 0u, bits_all,
                                rank_stride, world, n_prob, k, my_rank, out_count, w));
     return DC_OK;

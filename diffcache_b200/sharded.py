@@ -33,7 +33,7 @@ PAD = 0xFFFFFFFF
 class PeerExchange:
     """Exchange buffers of all ranks mapped into one another (CUDA IPC over ``torch.distributed``), for the
     fused exchange kernels behind ``dc_xchg_*`` / ``dc_sharded_*``: producers store their block into every
-    peer's buffer over NVLink and raise a flag, consumers poll their own buffer.  ``slot_bytes[c]`` is the
+    peer's buffer over NVLink as (word, epoch) pairs, consumers poll their own buffer.  ``slot_bytes[c]`` is the
     block size of channel ``c`` per rank (multiples of 16).
 
     Construction is collective.  If any rank cannot map a peer (no peer access, IPC not permitted) every
@@ -87,18 +87,6 @@ class PeerExchange:
                     _lib.check(a.lib.dc_xchg_set_peer(a._h, b.rank, a.lib.dc_xchg_local(b._h)))
         return xs
 
-    def channel_tensor(self, channel: int, dtype: torch.dtype) -> torch.Tensor:
-        """This rank's copy of a channel as a ``(world, slot_elems)`` tensor (no copy)."""
-        ptr = self.lib.dc_xchg_channel(self._h, channel)
-        n16 = self.slot_bytes[channel] // 2
-
-        class _Raw:
-            __cuda_array_interface__ = {"shape": (self.world, n16), "typestr": "<i2", "data": (int(ptr), False),
-                                        "version": 2}
-
-        t = torch.as_tensor(_Raw(), device=torch.device("cuda", self.device))
-        return t.view(dtype)
-
     def push(self, channel: int, src: torch.Tensor, stream=None) -> None:
         st = int(torch.cuda.current_stream().cuda_stream) if stream is None else int(stream)
         _lib.check(self.lib.dc_xchg_push(self._h, channel, src.data_ptr(), src.numel() * src.element_size(), st))
@@ -110,9 +98,11 @@ class PeerExchange:
         _lib.check(self.lib.dc_xchg_push_rows(self._h, channel, src.data_ptr(), rows,
                                               src.numel() // rows * src.element_size(), st))
 
-    def wait(self, channel: int, stream=None) -> None:
+    def collect(self, channel: int, dst: torch.Tensor, stream=None) -> None:
+        """Waits for the blocks of all ranks and writes them densely into ``dst`` (``world`` slots after
+        :meth:`push`, ``(rows, world, n)`` after :meth:`push_rows`); ``dst`` must be exactly what was pushed."""
         st = int(torch.cuda.current_stream().cuda_stream) if stream is None else int(stream)
-        _lib.check(self.lib.dc_xchg_wait(self._h, channel, st))
+        _lib.check(self.lib.dc_xchg_collect(self._h, channel, dst.data_ptr(), dst.numel() * dst.element_size(), st))
 
     def check(self) -> None:
         """Synchronises the current stream; raises if a wait for peer data ran out of time."""
@@ -299,8 +289,8 @@ class GpuShardBackend:
         return ptr(self.k_new), ptr(self.v_new), ptr(self.res_k), ptr(self.res_v), sb, sh, int(self.res_len)
 
     def peer_step(self, q, k, xchg: PeerExchange):
-        """The whole step as one call: scan, select, key push | wait, prefix count, attention, partial push |
-        wait, merge."""
+        """The whole step as one call: scan, select, key push | prefix count (polls the keys), attention, split
+        merge, partial push | merge (polls the partials).  ``k`` must be even."""
         out = self._buf("out", (self.e.bsz, self.e.q_head_num, self.D), torch.bfloat16 if self.e.dtype == 0 else torch.float16)
         kn, vn, rk, rv, sb, sh, rl = self._res_args()
         _lib.check(self.lib.dc_sharded_decode_attend(self.e._h, xchg._h, q.data_ptr(), kn, vn, rk, rv, sb, sh, rl, int(k),
@@ -324,7 +314,8 @@ class GpuShardBackend:
 
     def trace_step(self, q, k, xchg: PeerExchange):
         """One peer step with an event after every kernel; returns the intervals in microseconds, in order:
-        scan, select, key push, wait + prefix count, attention + split merge, partial push, wait + merge."""
+        scan, select, key push, prefix count (incl. its wait for the keys), attention + split merge, partial
+        push, merge (incl. its wait for the partials)."""
         _lib.check(self.lib.dc_trace_begin(self.e._h, 16))
         self.peer_step(q, k, xchg)
         vals = (ctypes.c_float * 16)()

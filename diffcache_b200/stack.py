@@ -13,8 +13,8 @@ rows of the fused projection, so scan / select / attend are local; the per-layer
 all-gather of the attention output slice ``(B, Hq/world * D)`` before a replicated output
 projection (deterministic: every rank computes the same residual stream).  That all-gather is
 either an NCCL call or (``exchange="peer"``) a push of the slice into every rank's buffer with
-stores over NVLink, interleaved so that the buffer reads ``(B, Hq*D)`` directly, plus a small wait
-kernel (:class:`diffcache_b200.sharded.PeerExchange`); consecutive layers use different channels of
+stores over NVLink, interleaved so that the buffer reads ``(B, Hq*D)``, plus a small kernel that waits
+for all slices and unpacks them (:class:`diffcache_b200.sharded.PeerExchange`); consecutive layers use different channels of
 the exchange so that a fast rank never overwrites a block a slow rank is still reading.
 """
 from __future__ import annotations
@@ -95,8 +95,9 @@ class AttentionStack:
                     slot = batch * self.q_local * head_dim * 2
                     self.xchg = PeerExchange([slot] * m, self.device.index, group)
                     self.xchg_channels = m
-                    self.xchg_views = [self.xchg.channel_tensor(c, dt).view(batch, self.world * self.q_local * head_dim)
-                                       for c in range(m)]
+                    # where the wait kernel unpacks a layer's gathered slices: (B, world * q_local * D)
+                    self.xchg_views = [torch.empty((batch, self.world * self.q_local * head_dim), dtype=dt,
+                                                   device=self.device) for _ in range(m)]
                 except RuntimeError:
                     if exchange == "peer":
                         raise
@@ -132,8 +133,8 @@ class AttentionStack:
                     dist.barrier(self.pg)
                 self._last_channel = ch
                 self.xchg.push_rows(ch, self.attn_local.view(B, -1))   # lands as (B, world, q_local*D) on every rank
-                self.xchg.wait(ch)
                 attn = self.xchg_views[ch]
+                self.xchg.collect(ch, attn)                           # waits for all slices, unpacks them densely
             elif self.world > 1:
                 dist.all_gather_into_tensor(self.attn_full.view(-1), self.attn_local.view(-1), group=self.pg)
                 attn = self.attn_full.view(self.world, B, self.kv_local, -1).permute(1, 0, 2, 3).reshape(B, -1)

@@ -302,27 +302,33 @@ int dc_attend_owned(dc_engine* e, const void* q, const uint32_t* sel_gidx, int n
  * No counterpart in the reference (single process, single GPU).
  *
  * Set-up, once: every rank calls dc_xchg_create (its own buffer: per channel
- * `world` slots of slot_bytes[c] bytes, multiples of 16), hands the
+ * `world` slots of slot_bytes[c] payload bytes, multiples of 16), hands the
  * dc_xchg_handle_bytes()-byte handle of dc_xchg_get_handle to every other rank
  * over any side channel (it is a cudaIpcMemHandle_t), and maps each peer with
  * dc_xchg_open_peer; ranks that live in the same process use dc_xchg_set_peer
  * with dc_xchg_local() of the peer instead.  All ranks must have finished this
  * before the first push (a host barrier).
  *
- * dc_xchg_push(channel, src, bytes): stores `bytes` (multiple of 16) from device
- * memory `src` into slot `rank` of the channel in EVERY rank's buffer, then
- * publishes a new epoch in every rank's flag word for (channel, rank).
+ * Wire format: every 32-bit word is stored as an 8-byte pair {word, epoch}; a
+ * reader that finds the epoch it expects has the word that came with it, so
+ * arrival needs no fence and no separate flag.
+ * dc_xchg_push(channel, src, bytes): sends `bytes` (multiple of 16) from device
+ * memory `src` into slot `rank` of the channel in EVERY rank's buffer, tagged
+ * with the channel's next epoch.
  * dc_xchg_push_rows(channel, src, rows, row_bytes): the same for a (rows,
  * row_bytes) block that is to be interleaved with the other ranks' blocks row by
- * row: afterwards the channel reads as (rows, world, row_bytes), i.e. as the
- * concatenation along the last axis (an all-gather of head slices).
- * dc_xchg_wait(channel): a kernel that returns once the blocks of the current
- * epoch of all ranks have arrived in this rank's buffer (dc_xchg_channel gives
- * the local address: slot r at offset r * slot_bytes).  Every rank must issue
- * the same sequence of pushes.  Waits are bounded (2 s by default,
- * dc_xchg_set_timeout_ms or the environment variable DC_XCHG_TIMEOUT_MS): when
- * one runs out, the kernel records a status and finishes, and dc_xchg_check
- * (synchronises `stream`) returns DC_EDEVICE — a missing peer never hangs the GPU.
+ * row: the channel then holds (rows, world, row_bytes), i.e. the concatenation
+ * along the last axis (an all-gather of head slices).
+ * dc_xchg_collect(channel, dst, bytes): a kernel that waits until the first
+ * `bytes` payload bytes of this rank's copy of the channel carry the current
+ * epoch (every one of them must have been pushed in this exchange) and writes
+ * them densely to device memory `dst`.  The sharded step below does not need it:
+ * its consumer kernels read the pairs themselves.
+ * Every rank must issue the same sequence of pushes.  Waits are bounded (2 s by
+ * default, dc_xchg_set_timeout_ms or the environment variable
+ * DC_XCHG_TIMEOUT_MS): when one runs out, the kernel records a status, finishes
+ * on zeros, and dc_xchg_check (synchronises `stream`) returns DC_EDEVICE — a
+ * missing peer never hangs the GPU.
  * ------------------------------------------------------------------------- */
 typedef struct dc_xchg dc_xchg;
 int dc_xchg_create(int rank, int world, int device, const int64_t* slot_bytes, int n_channels, dc_xchg** out);
@@ -332,11 +338,10 @@ int dc_xchg_get_handle(dc_xchg* x, void* handle_out);
 int dc_xchg_open_peer(dc_xchg* x, int peer_rank, const void* handle);
 int dc_xchg_set_peer(dc_xchg* x, int peer_rank, void* peer_base);
 void* dc_xchg_local(dc_xchg* x);
-void* dc_xchg_channel(dc_xchg* x, int channel);
 int dc_xchg_set_timeout_ms(dc_xchg* x, int ms);
 int dc_xchg_push(dc_xchg* x, int channel, const void* src, int64_t bytes, uint64_t stream);
 int dc_xchg_push_rows(dc_xchg* x, int channel, const void* src, int64_t rows, int64_t row_bytes, uint64_t stream);
-int dc_xchg_wait(dc_xchg* x, int channel, uint64_t stream);
+int dc_xchg_collect(dc_xchg* x, int channel, void* dst, int64_t bytes, uint64_t stream);
 int dc_xchg_check(dc_xchg* x, uint64_t stream);
 
 /*
@@ -349,8 +354,8 @@ int dc_xchg_check(dc_xchg* x, uint64_t stream);
  *                       resident rows / new token as given there) and pushes the partial result;
  *   dc_sharded_combine  waits for all ranks' partials and merges them by log-sum-exp into `out`
  *                       (bsz, q_heads, head_dim), identical on every rank.
- * dc_sharded_decode_attend runs the three in a row: the whole step is one call and seven kernels on
- * `stream`, capturable in a CUDA graph once the first call has allocated the per-engine buffers.
+ * dc_sharded_decode_attend runs the three in a row: the whole step is one call and eight kernels on
+ * `stream` (topk must be even), capturable in a CUDA graph once the first call has allocated the per-engine buffers.
  * Results are those of dc_decode_attend on the concatenated rows (same ranking keys, ties to the
  * smaller global row id: nsw.rs:74-91,612).
  */

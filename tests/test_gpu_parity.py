@@ -787,7 +787,7 @@ def test_sequence_sharded_step_emulated_on_one_gpu(oracle_lib, n_r, topk, world)
 
 def test_peer_exchange_wait_runs_out_without_hanging():
     """A wait for a block that no rank sends returns after its time limit with an error status (the kernel
-    finishes, the context stays usable); once the block arrives the same wait succeeds."""
+    finishes, the context stays usable); once the block has arrived the same wait succeeds."""
     from diffcache_b200 import sharded
     from diffcache_b200._lib import DiffCacheError
 
@@ -795,25 +795,34 @@ def test_peer_exchange_wait_runs_out_without_hanging():
     x0, x1 = sharded.PeerExchange.in_process([256], [dev, dev])
     x0.set_timeout_ms(50)
     block = torch.arange(64, dtype=torch.int32, device="cuda")
+    got = torch.full((2, 64), -1, dtype=torch.int32, device="cuda")
     x0.push(0, block)          # rank 0 sends; rank 1 does not
-    x0.wait(0)                 # ... so rank 0's wait for rank 1's block runs out
+    x0.collect(0, got)         # ... so rank 0's wait for rank 1's block runs out
     with pytest.raises(DiffCacheError):
         x0.check()
+    torch.cuda.synchronize()
+    assert torch.equal(got[0], block) and int(got[1].abs().sum()) == 0   # what arrived is delivered, the rest is zeros
     x1.push(0, block + 100)    # now the missing block arrives
-    x0.wait(0)
+    x0.collect(0, got)
     x0.check()
     torch.cuda.synchronize()
-    got = x0.channel_tensor(0, torch.int32)
     assert torch.equal(got[0], block) and torch.equal(got[1], block + 100)
+    # a second exchange on the same channel: the first one's pairs carry the old epoch and are not taken for new data
+    x0.push(0, block + 7); x1.push(0, block + 9)
+    x0.collect(0, got)
+    x0.check()
+    torch.cuda.synchronize()
+    assert torch.equal(got[0], block + 7) and torch.equal(got[1], block + 9)
     # rows interleaved by rank: every rank's copy reads (rows, world, n)
     y0, y1 = sharded.PeerExchange.in_process([4 * 32], [dev, dev])
     a = torch.arange(32, dtype=torch.int32, device="cuda").view(4, 8)
     y0.push_rows(0, a); y1.push_rows(0, a + 1000)
-    y0.wait(0); y1.wait(0)
-    y0.check(); y1.check()
     want = torch.stack([a, a + 1000], dim=1)
     for y in (y0, y1):
-        assert torch.equal(y.channel_tensor(0, torch.int32).view(4, 2, 8), want)
+        out = torch.zeros((4, 2, 8), dtype=torch.int32, device="cuda")
+        y.collect(0, out)
+        y.check()
+        assert torch.equal(out, want)
     for x in (x0, x1, y0, y1):
         x.close()
 

@@ -9,7 +9,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(_HERE, "csrc")
 LIB_DIR = os.path.join(_HERE, "_lib")
 LIB_PATH = os.path.join(LIB_DIR, "libdiffcache_b200.so")
-SOURCES = ["scan.cu", "select.cu", "attend.cu", "pq.cu", "budget.cu", "exchange.cu", "engine.cu"]
+SOURCES = ["scan.cu", "scan_tc.cu", "select.cu", "attend.cu", "pq.cu", "budget.cu", "exchange.cu", "engine.cu"]
 HEADERS = [os.path.join(CSRC, "common.cuh"), os.path.join(CSRC, "exchange.cuh"),
            os.path.join(_HERE, "..", "include", "diffcache_b200.h")]
 

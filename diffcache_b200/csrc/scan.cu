@@ -7,7 +7,8 @@
 // there is no dense contraction to hand to the tensor cores), and the only thing written back
 // is one 4-byte ranking key per row (1.6 % of the bytes read).
 //
-// Three kernels compute the same thing (selected by the environment variable DC_SCAN_VARIANT):
+// Four kernels compute the same thing (selected by the environment variable DC_SCAN_VARIANT; the fourth,
+// "tcgen05" — TMA-fed tensor-core tiles with the accumulator in tensor memory — lives in scan_tc.cu):
 //   "wide"   (default) 32-byte global loads, each warp-wide load covers 1 KB of consecutive rows;
 //   "narrow" 16-byte global loads (512 B per warp-wide load);
 //   "tma"    rows brought in by the TMA engine, one 32 KB cp.async.bulk per stage of a shared-memory
@@ -21,6 +22,10 @@
 #include "common.cuh"
 
 namespace dc {
+
+int score_scan_tc(const void* keys, int64_t prob_stride, int n_prob, int64_t n, const int32_t* n_dev, int head_dim, int dtype,
+                  const void* q, int q_mode, int group, int kv_heads, int64_t q_stride_b, uint32_t* scores,
+                  int64_t score_stride, uint32_t* minmax, uint32_t* status, cudaStream_t stream);
 
 namespace {
 
@@ -364,7 +369,12 @@ int launch_scan(const void* keys, int64_t prob_stride, int n_prob, int64_t n, co
     int rows_per_cta = ((rows_cfg + kScanWarps * TR - 1) / (kScanWarps * TR)) * (kScanWarps * TR);
     int64_t chunks = (n + rows_per_cta - 1) / rows_per_cta;
     dim3 grid(static_cast<unsigned>(chunks), static_cast<unsigned>(n_prob));
-    const char* variant = std::getenv("DC_SCAN_VARIANT");  // read per call: "wide" (default), "narrow", "tma"
+    const char* variant = std::getenv("DC_SCAN_VARIANT");  // read per call: "wide" (default), "narrow", "tma", "tcgen05"
+    if (variant != nullptr && std::strcmp(variant, "tcgen05") == 0) {
+        const int rc = score_scan_tc(keys, prob_stride, n_prob, n, n_dev, LPR * 8, DT, q, q_mode, group, kv_heads, q_stride_b,
+                                     scores, score_stride, minmax, status, stream);
+        if (rc != DC_ESTATE) return rc;   // DC_ESTATE: not applicable to this shape, use the default kernel
+    }
     const bool want_tma = variant != nullptr && std::strcmp(variant, "tma") == 0;
     const bool want_narrow = variant != nullptr && std::strcmp(variant, "narrow") == 0;
     if (want_tma) {

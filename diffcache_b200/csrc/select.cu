@@ -525,12 +525,28 @@ topk_select_kernel(const uint32_t* __restrict__ bits, const uint32_t* __restrict
         if (cc > kCandCap || cc < need) {
             if (tid == 0) ctl.error = 2;
         } else {
-            int cpad = 1;
-            while (cpad < static_cast<int>(cc)) cpad <<= 1;
-            for (int i = cc + tid; i < cpad; i += kSelThreads) s_cand[i] = ~0ull;
-            __syncthreads();
-            bitonic_sort_u64(s_cand, cpad);
-            for (uint32_t i = tid; i < need; i += kSelThreads) s_out[base_out + i] = s_cand[i];
+            if (cc <= 384) {
+                // few keys in the threshold bin (the usual case): the place of a key among them is the number of
+                // smaller keys (keys are unique, the row id is part of them) — one pass of broadcast reads
+                // instead of the ~30 barrier-separated stages of a bitonic sort
+                __syncthreads();
+                for (uint32_t i = tid; i < cc; i += kSelThreads) {
+                    const unsigned long long key = s_cand[i];
+                    uint32_t rank = 0;
+                    for (uint32_t j = 0; j < cc; j++) {
+                        const unsigned long long other = s_cand[j];
+                        rank += (other < key || (other == key && j < i)) ? 1u : 0u;   // (identical pad entries keep their order)
+                    }
+                    if (rank < need) s_out[base_out + rank] = key;
+                }
+            } else {
+                int cpad = 1;
+                while (cpad < static_cast<int>(cc)) cpad <<= 1;
+                for (int i = cc + tid; i < cpad; i += kSelThreads) s_cand[i] = ~0ull;
+                __syncthreads();
+                bitonic_sort_u64(s_cand, cpad);
+                for (uint32_t i = tid; i < need; i += kSelThreads) s_out[base_out + i] = s_cand[i];
+            }
         }
     }
     __syncthreads();

@@ -95,6 +95,36 @@ def test_scan_variants_agree(lib, monkeypatch, dtype, D):
     assert np.array_equal(got["tma"][0], got["narrow"][0]) and np.array_equal(got["tma"][1], got["narrow"][1])
 
 
+@pytest.mark.parametrize("dtype", ["bf16", "fp16"])
+def test_scan_tensor_core_variant(lib, oracle_lib, monkeypatch, dtype):
+    """DC_SCAN_VARIANT=tcgen05 (TMA tiles, tcgen05.mma, accumulator in tensor memory; head_dim 128): ranking
+    keys within one ulp of dist of the oracle's, the same min/max folding, ragged sizes around the 128-row
+    tile, several problems per CTA and several CTAs per problem; the kernel's status word stays clear."""
+    dt = util.dtype_code(dtype)
+    D = 128
+    for P_shape, n in (((1, 3), 1), ((1, 3), 127), ((1, 3), 128), ((1, 3), 129), ((2, 4), 5000), ((40, 8), 300),
+                       ((1, 2), 70001)):
+        B, Hkv = P_shape
+        P = B * Hkv
+        k, _, q = util.small_problem(B, Hkv, 4, n, D, seed=900 + n, dtype=dtype)
+        kd, qd = k.cuda().reshape(P, n, D), q.cuda().contiguous()
+        monkeypatch.setenv("DC_SCAN_VARIANT", "tcgen05")
+        bits_tc, mm_tc = _scan(lib, kd, qd, n, D, dt, 1, 4)
+        monkeypatch.delenv("DC_SCAN_VARIANT")
+        bits_ref, mm_ref = _scan(lib, kd, qd, n, D, dt, 1, 4)
+        ku = util.u16(k).reshape(P, n, D)
+        qm = oracle_lib.group_mean(util.u16(q).reshape(-1, D), 4, dt)
+        for p in range(0, P, max(1, P // 5)):
+            want = oracle_lib.score_rows(ku[p], qm[p], dt)
+            diff = np.abs(bits_tc[p].view(np.float32).astype(np.float64) - want.view(np.float32).astype(np.float64))
+            assert np.all(diff <= util.ulp_of_dist(want)), f"n={n} p={p}: worst {diff.max()}"
+            assert np.mean(bits_tc[p] == want) > 0.9 or n < 64
+        a = bits_tc.view(np.float32).astype(np.float64)
+        b = bits_ref.view(np.float32).astype(np.float64)
+        assert np.all(np.abs(a - b) <= util.ulp_of_dist(bits_ref))
+        assert np.array_equal(mm_tc[:, 0], bits_tc.min(axis=1)) and np.array_equal(mm_tc[:, 1], bits_tc.max(axis=1))
+
+
 def test_scan_group_mean_matches_torch_cuda_mean(lib):
     """q_mode 1 (mean formed in the kernel) must equal scanning with torch's CUDA mean, the
     operation the reference runs at src/diffcache/kvcache/diffcache.py:193 — bit for bit."""

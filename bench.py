@@ -127,6 +127,8 @@ class Ranks:
             import torch.distributed as dist
 
             os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+            if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
+                os.environ["NCCL_DEBUG"] = "WARN"   # keep NCCL's version banner off stdout: one JSON line only
             torch.cuda.set_device(self.local)
             dist.init_process_group("nccl", device_id=torch.device("cuda", self.local))
         else:
@@ -640,7 +642,7 @@ def run_seq_sharded(cfg, ranks: Ranks, steps, warmup):
                  "ms_per_step_cuda_graph": float(np.median(graph_loops)) if graph_loops else None,
                  "timing": summarise(graph_loops if graph_loops else stream_loops),
                  "collectives_per_step": (2 if world > 1 else 0) if mode == "nccl" else 0,
-                 "kernels_per_step": 8 if mode == "peer" else 6}
+                 "kernels_per_step": 6}
         entry["ms_per_step"] = entry["ms_per_step_cuda_graph"] or entry["ms_per_step_stream_launch"]
         if mode == "peer":
             ranks.barrier()
@@ -650,8 +652,10 @@ def run_seq_sharded(cfg, ranks: Ranks, steps, warmup):
             tr = np.median(np.array(traces), axis=0) if traces and len(traces[0]) == 7 else None
             if tr is not None:
                 tr = ranks.max_over_ranks(tr.tolist())
-                names = ("scan", "select", "push_keys", "wait_keys+prefix_count", "attend+split_merge", "push_partials",
-                         "wait_partials+merge")
+                # the two "push" intervals are empty unless DC_XCHG_FUSED=0 moves the exchange stores out of the
+                # select / split-merge kernels into copy kernels of their own
+                names = ("scan", "select+push_keys", "push_keys_kernel", "wait_keys+prefix_count",
+                         "attend+split_merge+push_partials", "push_partials_kernel", "wait_partials+merge")
                 entry["phases_us"] = {n: round(float(x), 2) for n, x in zip(names, tr)}
                 entry["phases_us"]["sum"] = round(float(sum(tr)), 2)
                 entry["phases_us"]["note"] = ("CUDA events after every kernel of a stream-launched step, median of 20, "

@@ -435,9 +435,12 @@ __global__ void __launch_bounds__(kCombineThreads)
 lse_combine_kernel(const float* __restrict__ part_acc, int64_t acc_ps, int64_t acc_rs,
                    const float* __restrict__ part_ml, int64_t ml_ps, int64_t ml_rs, int n_part, int dim,
                    uint16_t* __restrict__ out, float* __restrict__ out_lse, float* __restrict__ out_acc,
-                   float* __restrict__ out_ml, const XchgLL ll, int64_t ll_ml_off) {
+                   float* __restrict__ out_ml, const XchgLL ll, int64_t ll_ml_off, const XchgOut xo, int64_t xo_ml_off) {
     pdl_launch_dependents();
     pdl_wait();
+    // results that other ranks need go straight into every rank's exchange buffer as well (pair format):
+    // (acc, m, l) of a sequence-sharded step, or the 16-bit output slice of a head-sharded layer
+    const uint32_t xepoch = xo.world ? xchg_next_epoch(xo) : 0u;
     const int64_t row = blockIdx.x;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     __shared__ float s_w[kCombineMaxParts];   // weight of every part: exp2(m_s - M)
@@ -524,11 +527,23 @@ lse_combine_kernel(const float* __restrict__ part_acc, int64_t acc_ps, int64_t a
                 t.x += p4.x; t.y += p4.y; t.z += p4.z; t.w += p4.w;
             }
             const float v4[4] = {t.x, t.y, t.z, t.w};
+            uint16_t e4[4];
 #pragma unroll
             for (int j = 0; j < 4; j++) {
                 const int d = 4 * tid + j;
-                if (out) out[row * dim + d] = float_to_elem<DT>(L > 0.0f ? v4[j] / L : 0.0f);
+                e4[j] = float_to_elem<DT>(L > 0.0f ? v4[j] / L : 0.0f);
+                if (out) out[row * dim + d] = e4[j];
                 if (out_acc) out_acc[row * dim + d] = v4[j];
+            }
+            if (xo.world) {
+                if (out_acc) {   // four fp32 accumulators = four words
+                    const int64_t w = xchg_word_index(xo, row, 4 * tid);
+                    xchg_put2(xo, xepoch, w, __float_as_uint(v4[0]), __float_as_uint(v4[1]));
+                    xchg_put2(xo, xepoch, w + 2, __float_as_uint(v4[2]), __float_as_uint(v4[3]));
+                } else {         // four 16-bit outputs = two words
+                    xchg_put2(xo, xepoch, xchg_word_index(xo, row, 2 * tid), e4[0] | (static_cast<uint32_t>(e4[1]) << 16),
+                              e4[2] | (static_cast<uint32_t>(e4[3]) << 16));
+                }
             }
         }
     } else {
@@ -537,12 +552,16 @@ lse_combine_kernel(const float* __restrict__ part_acc, int64_t acc_ps, int64_t a
             for (int s = 0; s < n_part; s++) o += acc[s * acc_ps + d] * s_w[s];
             if (out) out[row * dim + d] = float_to_elem<DT>(L > 0.0f ? o / L : 0.0f);
             if (out_acc) out_acc[row * dim + d] = o;
+            if (xo.world && out_acc) xchg_put(xo, xepoch, xchg_word_index(xo, row, d), __float_as_uint(o));
         }
+        // (the host only asks for a fan-out of 16-bit outputs when the vector path above is taken)
     }
     if (tid == 0) {
         if (out_lse) out_lse[row] = L > 0.0f ? (M + log2f(L)) * 0.6931471805599453f : -INFINITY;
         if (out_ml) { out_ml[row * 2] = M; out_ml[row * 2 + 1] = L; }
+        if (xo.world && out_ml) xchg_put2(xo, xepoch, xo.rank_off + xo_ml_off + row * 2, __float_as_uint(M), __float_as_uint(L));
     }
+    if (xo.world) xchg_finish(xo, xepoch, gridDim.x);
 }
 
 template <int DT, int LPR>
@@ -584,8 +603,13 @@ int64_t attend_scratch_bytes(int n_prob, int group, int head_dim) {
 
 int lse_combine(const float* acc, int64_t acc_ps, int64_t acc_rs, const float* ml, int64_t ml_ps, int64_t ml_rs,
                 int n_part, int64_t rows, int head_dim, int dtype, void* out, float* out_lse, float* out_acc,
-                float* out_ml, cudaStream_t stream, const XchgLL* ll) {
+                float* out_ml, cudaStream_t stream, const XchgLL* ll, const XchgOut* xout) {
     // ll (may be NULL): the parts arrive in pair format in an exchange channel instead of acc / ml
+    // xout (may be NULL): the results are also stored into every rank's copy of an exchange channel, either
+    // (out_acc, out_ml) as [acc (rows, dim) | ml (rows, 2)] words or `out` as 16-bit pairs, laid out by xout
+    DC_REQUIRE(xout == nullptr || out_acc != nullptr ||
+                   (head_dim % 4 == 0 && head_dim / 4 <= kCombineThreads && kCombineThreads % (head_dim / 4) == 0),
+               "lse_combine: fan-out of 16-bit outputs needs head_dim a multiple of 4 that divides %d", 4 * kCombineThreads);
     DC_REQUIRE(((acc && ml) || ll) && n_part >= 1 && rows >= 0, "lse_combine: bad arguments");
     DC_REQUIRE(ll == nullptr || (n_part <= kXchgMaxWorld && head_dim <= 256 && head_dim % 2 == 0),
                "lse_combine: parts from the peer exchange: at most %d parts, even head_dim <= 256", kXchgMaxWorld);
@@ -595,13 +619,17 @@ int lse_combine(const float* acc, int64_t acc_ps, int64_t acc_rs, const float* m
     const dim3 grid(static_cast<unsigned>(rows)), block(kCombineThreads);
     XchgLL w = {};
     if (ll != nullptr) w = *ll;
+    XchgOut xo = {};
+    if (xout != nullptr) xo = *xout;
     const int64_t ml_off = rows * head_dim;   // word offset of the (m, l) block inside a part's slot
     if (dtype == DC_BF16)
         DC_CUDA_TRY(launch_chained(lse_combine_kernel<DC_BF16>, grid, block, 0, stream, 0u, acc, acc_ps, acc_rs, ml, ml_ps,
-                                   ml_rs, n_part, head_dim, static_cast<uint16_t*>(out), out_lse, out_acc, out_ml, w, ml_off));
+                                   ml_rs, n_part, head_dim, static_cast<uint16_t*>(out), out_lse, out_acc, out_ml, w, ml_off,
+                                   xo, ml_off));
     else
         DC_CUDA_TRY(launch_chained(lse_combine_kernel<DC_FP16>, grid, block, 0, stream, 0u, acc, acc_ps, acc_rs, ml, ml_ps,
-                                   ml_rs, n_part, head_dim, static_cast<uint16_t*>(out), out_lse, out_acc, out_ml, w, ml_off));
+                                   ml_rs, n_part, head_dim, static_cast<uint16_t*>(out), out_lse, out_acc, out_ml, w, ml_off,
+                                   xo, ml_off));
     return DC_OK;
 }
 
@@ -611,7 +639,7 @@ int sparse_attend(const void* k_store, const void* v_store, int64_t prob_stride,
                   void* res_v, int64_t res_stride_b, int64_t res_stride_h, int res_len, float scale, void* out,
                   float* out_lse, float* out_acc, float* out_ml, void* scratch, cudaStream_t stream,
                   const int32_t* sel_count, int64_t q_stride_b, int64_t new_stride_b, const int32_t* n_rows_dev,
-                  const int32_t* res_len_dev) {
+                  const int32_t* res_len_dev, const XchgOut* xout) {
     // n_rows_dev / res_len_dev (may be NULL): device words read when the kernel runs, overriding n_rows and
     // res_len, which then only size the launch (res_len = the most resident rows there can be)
     DC_REQUIRE(q != nullptr && scratch != nullptr, "sparse_attend: null q/scratch");
@@ -682,7 +710,7 @@ int sparse_attend(const void* k_store, const void* v_store, int64_t prob_stride,
     if (rc != DC_OK) return rc;
     return lse_combine(a.part_acc, head_dim, static_cast<int64_t>(a.n_split) * head_dim, a.part_ml, 2,
                        static_cast<int64_t>(a.n_split) * 2, a.n_split, static_cast<int64_t>(n_prob) * group, head_dim,
-                       dtype, out, out_lse, out_acc, out_ml, stream, nullptr);
+                       dtype, out, out_lse, out_acc, out_ml, stream, nullptr, xout);
 }
 
 }  // namespace dc
@@ -762,5 +790,6 @@ extern "C" int dc_sparse_attend_noalloc(const void* k_store, const void* v_store
     if (rc != DC_OK) return rc;
     return sparse_attend(k_store, v_store, prob_stride, n_rows, n_prob, kv_heads, group, head_dim, dtype, q, sel,
                          sel_stride, n_sel, sel_base, k_new, v_new, res_k, res_v, res_stride_b, res_stride_h, res_len,
-                         scale, out, out_lse, out_acc, out_ml, scratch, as_stream(stream), nullptr, 0, 0, nullptr, nullptr);
+                         scale, out, out_lse, out_acc, out_ml, scratch, as_stream(stream), nullptr, 0, 0, nullptr, nullptr,
+                         nullptr);
 }

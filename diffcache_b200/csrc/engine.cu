@@ -22,7 +22,8 @@ int score_scan(const void* keys, int64_t prob_stride, int n_prob, int64_t n, int
                uint32_t* status = nullptr, int kv_heads = 1, int64_t q_stride_b = 0, const int32_t* n_dev = nullptr);
 int topk_select(const uint32_t* bits, const uint32_t* ids, int64_t in_stride, int n_prob, int64_t n, int k,
                 const uint32_t* minmax, uint32_t id_offset, uint32_t* out_bits, uint32_t* out_ids, int64_t out_stride,
-                uint32_t* status, cudaStream_t stream, uint32_t* minmax_reset = nullptr, const int32_t* n_dev = nullptr);
+                uint32_t* status, cudaStream_t stream, uint32_t* minmax_reset = nullptr, const int32_t* n_dev = nullptr,
+                const XchgOut* xout = nullptr);
 int select_prepare();
 int64_t select_scratch_bytes(int n_prob);
 int merge_sorted_count(const uint32_t* bits_all, int world, int n_prob, int k, int my_rank, int32_t* out_count,
@@ -33,13 +34,13 @@ int sparse_attend(const void* k_store, const void* v_store, int64_t prob_stride,
                   void* res_v, int64_t res_stride_b, int64_t res_stride_h, int res_len, float scale, void* out,
                   float* out_lse, float* out_acc, float* out_ml, void* scratch, cudaStream_t stream,
                   const int32_t* sel_count = nullptr, int64_t q_stride_b = 0, int64_t new_stride_b = 0,
-                  const int32_t* n_rows_dev = nullptr, const int32_t* res_len_dev = nullptr);
+                  const int32_t* n_rows_dev = nullptr, const int32_t* res_len_dev = nullptr, const XchgOut* xout = nullptr);
 int adaptive_budget(const uint32_t* bits, int64_t stride, int n_prob, int k, int head_dim, const int* seq, int n_seq,
                     float threshold, int32_t* budget, cudaStream_t stream, const int32_t* n_dev = nullptr);
 int64_t attend_scratch_bytes(int n_prob, int group, int head_dim);
 int lse_combine(const float* acc, int64_t acc_ps, int64_t acc_rs, const float* ml, int64_t ml_ps, int64_t ml_rs,
                 int n_part, int64_t rows, int head_dim, int dtype, void* out, float* out_lse, float* out_acc,
-                float* out_ml, cudaStream_t stream, const XchgLL* ll = nullptr);
+                float* out_ml, cudaStream_t stream, const XchgLL* ll = nullptr, const XchgOut* xout = nullptr);
 int pq_build_lut(const void* q, int q_mode, int group, int dtype, const float* centroids, int n_prob, int head_dim,
                  int n_sub, float* lut, cudaStream_t stream);
 int pq_adc_scan(const uint8_t* codes, int64_t prob_stride, int n_prob, int64_t n, int n_sub, const float* lut,
@@ -240,6 +241,8 @@ struct dc_engine {
     int32_t* shard_count = nullptr;   // (n_prob) length of the globally winning prefix
     float* shard_part = nullptr;      // [acc (rows, D) | ml (rows, 2)] partial attention of this rank
     int shard_k = 0;
+    dc_xchg* out_xchg = nullptr;      // dc_set_output_exchange: decode steps also fan their output slice out to it
+    int out_xchg_channel = 0;
     int64_t prob_stride = 0;   // elements
     int64_t score_stride = 0;  // elements
     uint16_t* k = nullptr;
@@ -338,7 +341,7 @@ int trace_mark(dc_engine* e, cudaStream_t s) {
 
 int scan_and_select(dc_engine* e, const void* q, int q_mode, int k, int64_t n_bound, uint32_t id_offset,
                     uint32_t* out_bits, uint32_t* out_ids, cudaStream_t s, cudaEvent_t* ev = nullptr,
-                    int64_t q_stride_b = 0) {
+                    int64_t q_stride_b = 0, const XchgOut* xout = nullptr) {
     // e->minmax is in its initial state here: set once in dc_create, and put back by every select
     if (ev) DC_CUDA_TRY(cudaEventRecord(ev[0], s));
     trace_mark(e, s);
@@ -348,7 +351,7 @@ int scan_and_select(dc_engine* e, const void* q, int q_mode, int k, int64_t n_bo
     if (ev) DC_CUDA_TRY(cudaEventRecord(ev[1], s));
     trace_mark(e, s);
     rc = topk_select(e->scores, nullptr, e->score_stride, e->n_prob, n_bound, k, e->minmax, id_offset, out_bits,
-                     out_ids, k, e->status, s, e->minmax, e->len);
+                     out_ids, k, e->status, s, e->minmax, e->len, xout);
     if (rc) return rc;
     if (ev) DC_CUDA_TRY(cudaEventRecord(ev[2], s));
     trace_mark(e, s);
@@ -727,10 +730,21 @@ int decode_attend_impl(dc_engine* e, const void* q, int64_t q_stride_b, const vo
         if (rc) return rc;
         sel_count = e->budget;
     }
+    XchgOut xo;
+    const XchgOut* xout = nullptr;
+    if (e->out_xchg != nullptr) {   // head-sharded layer: (bsz, q_heads, D) becomes (bsz, world, q_heads * D) on every rank
+        xo = xchg_out_args(e->out_xchg, e->out_xchg_channel);
+        const int64_t slice_words = static_cast<int64_t>(e->q_heads) * e->head_dim / 2;
+        xo.rows_per_block = e->q_heads;
+        xo.block_stride = xchg_world(e->out_xchg) * slice_words;
+        xo.rank_off = xchg_rank(e->out_xchg) * slice_words;
+        xo.row_words = e->head_dim / 2;
+        xout = &xo;
+    }
     rc = sparse_attend(e->k, e->v, e->prob_stride, bound, e->n_prob, e->kv_heads, e->group, e->head_dim, e->dtype,
                        q, e->sel_idx, k, k, 0, k_new, v_new, res_k, res_v, res_stride_b, res_stride_h, res_len, scale,
                        out, out_lse, nullptr, nullptr, e->att_scratch, s, sel_count, q_stride_b, new_stride_b, e->len,
-                       res_len_dev);
+                       res_len_dev, xout);
     if (rc) return rc;
     if (ev) {
         DC_CUDA_TRY(cudaEventRecord(ev[3], s));
@@ -870,8 +884,19 @@ int dc_trace_read(dc_engine* e, float* intervals_ms, int* n_marks) {
     return DC_OK;
 }
 
+static int local_topk_impl(dc_engine* e, const void* q, int topk, uint32_t* out_bits, uint32_t* out_gidx, uint64_t stream,
+                          const XchgOut* xout, bool* fanned_out);
+
 int dc_local_topk(dc_engine* e, const void* q, int topk, uint32_t* out_bits, uint32_t* out_gidx, uint64_t stream) {
+    return local_topk_impl(e, q, topk, out_bits, out_gidx, stream, nullptr, nullptr);
+}
+
+// xout: also store the keys into every rank's exchange buffer; *fanned_out tells whether that happened (it does
+// not when this engine holds no rows: the pads are then written by a memset, which cannot fan out).
+static int local_topk_impl(dc_engine* e, const void* q, int topk, uint32_t* out_bits, uint32_t* out_gidx, uint64_t stream,
+                          const XchgOut* xout, bool* fanned_out) {
     DC_ENGINE_ENTER(e);
+    if (fanned_out) *fanned_out = false;
     DC_REQUIRE(q && out_bits && out_gidx, "dc_local_topk: null pointer");
     DC_REQUIRE(topk >= 1 && topk <= DC_MAX_TOPK, "dc_local_topk: topk=%d outside [1, %d]", topk, DC_MAX_TOPK);
     cudaStream_t s = as_stream(stream);
@@ -883,13 +908,27 @@ int dc_local_topk(dc_engine* e, const void* q, int topk, uint32_t* out_bits, uin
         DC_CUDA_TRY(cudaMemsetAsync(out_gidx, 0xFF, static_cast<size_t>(e->n_prob) * topk * sizeof(uint32_t), s));
         return DC_OK;
     }
-    return scan_and_select(e, q, 1, topk, bound, static_cast<uint32_t>(e->row_offset), out_bits, out_gidx, s);
+    if (fanned_out) *fanned_out = xout != nullptr;
+    return scan_and_select(e, q, 1, topk, bound, static_cast<uint32_t>(e->row_offset), out_bits, out_gidx, s, nullptr, 0, xout);
 }
+
+static int attend_owned_impl(dc_engine* e, const void* q, const uint32_t* sel_gidx, int n_sel, const void* k_new,
+                            const void* v_new, void* res_k, void* res_v, int64_t res_stride_b, int64_t res_stride_h,
+                            int res_len, float scale, float* out_acc, float* out_ml, const int32_t* sel_count,
+                            uint64_t stream, const XchgOut* xout);
 
 int dc_attend_owned(dc_engine* e, const void* q, const uint32_t* sel_gidx, int n_sel, const void* k_new,
                     const void* v_new, void* res_k, void* res_v, int64_t res_stride_b, int64_t res_stride_h,
                     int res_len, float scale, float* out_acc, float* out_ml, const int32_t* sel_count,
                     uint64_t stream) {
+    return attend_owned_impl(e, q, sel_gidx, n_sel, k_new, v_new, res_k, res_v, res_stride_b, res_stride_h, res_len, scale,
+                             out_acc, out_ml, sel_count, stream, nullptr);
+}
+
+static int attend_owned_impl(dc_engine* e, const void* q, const uint32_t* sel_gidx, int n_sel, const void* k_new,
+                            const void* v_new, void* res_k, void* res_v, int64_t res_stride_b, int64_t res_stride_h,
+                            int res_len, float scale, float* out_acc, float* out_ml, const int32_t* sel_count,
+                            uint64_t stream, const XchgOut* xout) {
     DC_ENGINE_ENTER(e);
     DC_REQUIRE(q && out_acc && out_ml, "dc_attend_owned: null pointer");
     int64_t bound = 0;
@@ -898,10 +937,35 @@ int dc_attend_owned(dc_engine* e, const void* q, const uint32_t* sel_gidx, int n
     return sparse_attend(e->k, e->v, e->prob_stride, bound, e->n_prob, e->kv_heads, e->group, e->head_dim,
                          e->dtype, q, sel_gidx, n_sel, n_sel, e->row_offset, k_new, v_new, res_k, res_v, res_stride_b,
                          res_stride_h, res_len, scale, nullptr, nullptr, out_acc, out_ml, e->att_scratch,
-                         as_stream(stream), sel_count, 0, 0, e->len, nullptr);
+                         as_stream(stream), sel_count, 0, 0, e->len, nullptr, xout);
 }
 
 // ---- sequence-sharded step with the two exchanges done by peer stores (exchange.cu) ----
+
+// DC_XCHG_FUSED=0 keeps the exchange stores in separate copy kernels (for comparison); default: fused into the
+// kernels that produce the values.
+static bool fused_push() {
+    static const bool on = [] {
+        const char* v = std::getenv("DC_XCHG_FUSED");
+        return !(v != nullptr && v[0] == '0');
+    }();
+    return on;
+}
+
+int dc_set_output_exchange(dc_engine* e, dc_xchg* x, int channel) {
+    DC_ENGINE_ENTER(e);
+    if (x != nullptr) {
+        DC_REQUIRE(channel >= 0 && channel < kXchgChannels, "dc_set_output_exchange: channel %d", channel);
+        DC_REQUIRE(xchg_slot_bytes(x, channel) == static_cast<int64_t>(e->bsz) * e->q_heads * e->head_dim * 2,
+                   "dc_set_output_exchange: the channel's slot (%lld bytes) is not one (bsz, q_heads, head_dim) output slice",
+                   static_cast<long long>(xchg_slot_bytes(x, channel)));
+        DC_REQUIRE(e->head_dim % 4 == 0, "dc_set_output_exchange: head_dim");
+        DC_REQUIRE(xchg_ready(x), "dc_set_output_exchange: not every peer buffer is mapped yet");
+    }
+    e->out_xchg = x;
+    e->out_xchg_channel = channel;
+    return DC_OK;
+}
 
 static int64_t shard_part_bytes(const dc_engine* e) {
     const int64_t rows = static_cast<int64_t>(e->n_prob) * e->group;
@@ -943,10 +1007,16 @@ int dc_sharded_local(dc_engine* e, dc_xchg* x, const void* q, int topk, uint64_t
         DC_CUDA_TRY(cudaMemset(e->shard_part, 0, need[1]));
         e->shard_k = topk;
     }
-    int rc = dc_local_topk(e, q, topk, e->shard_bits, e->shard_gidx, stream);
+    // the select writes the sorted keys into every rank's buffer itself; only an engine without rows (pads
+    // written by a memset) needs the separate push
+    const XchgOut xo = xchg_out_args(x, 0);
+    bool fanned = false;
+    int rc = local_topk_impl(e, q, topk, e->shard_bits, e->shard_gidx, stream, fused_push() ? &xo : nullptr, &fanned);
     if (rc) return rc;
-    rc = dc_xchg_push(x, 0, e->shard_bits, need[0], stream);
-    if (rc) return rc;
+    if (!fanned) {
+        rc = dc_xchg_push(x, 0, e->shard_bits, need[0], stream);
+        if (rc) return rc;
+    }
     return trace_mark(e, s);
 }
 
@@ -962,12 +1032,18 @@ int dc_sharded_attend(dc_engine* e, dc_xchg* x, const void* q, const void* k_new
     if (rc) return rc;
     trace_mark(e, s);
     const int64_t rows = static_cast<int64_t>(e->n_prob) * e->group;
-    rc = dc_attend_owned(e, q, e->shard_gidx, k, k_new, v_new, res_k, res_v, res_stride_b, res_stride_h, res_len, scale,
-                         e->shard_part, e->shard_part + rows * e->head_dim, e->shard_count, stream);
+    // the split merge writes (acc, m, l) into every rank's buffer itself
+    XchgOut xo = xchg_out_args(x, 1);
+    xo.row_words = e->head_dim;
+    rc = attend_owned_impl(e, q, e->shard_gidx, k, k_new, v_new, res_k, res_v, res_stride_b, res_stride_h, res_len, scale,
+                           e->shard_part, e->shard_part + rows * e->head_dim, e->shard_count, stream,
+                           fused_push() ? &xo : nullptr);
     if (rc) return rc;
     trace_mark(e, s);
-    rc = dc_xchg_push(x, 1, e->shard_part, shard_part_bytes(e), stream);
-    if (rc) return rc;
+    if (!fused_push()) {
+        rc = dc_xchg_push(x, 1, e->shard_part, shard_part_bytes(e), stream);
+        if (rc) return rc;
+    }
     return trace_mark(e, s);
 }
 

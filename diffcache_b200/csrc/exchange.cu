@@ -19,6 +19,7 @@
 // host (dc_xchg_check), never as a hung GPU.
 //
 // The reference has no counterpart (single process, single GPU: src/diffcache/base.py:28).
+#include <cstdint>
 #include <cstdlib>
 #include <cstring>
 
@@ -133,6 +134,20 @@ XchgLL xchg_ll_args(const dc_xchg* x, int channel) {
     w.world = x->world;
     w.timeout_ns = x->timeout_ns;
     return w;
+}
+
+XchgOut xchg_out_args(const dc_xchg* x, int channel) {
+    XchgOut o;
+    for (int r = 0; r < kXchgMaxWorld; r++) o.chan[r] = r < x->world ? x->peer[r] + x->chan_off[channel] : nullptr;
+    o.world = x->world;
+    o.channel = channel;
+    o.epoch = x->words;
+    o.done = x->words + kXchgChannels;
+    o.rows_per_block = INT64_MAX;
+    o.block_stride = 0;
+    o.rank_off = static_cast<int64_t>(x->rank) * (x->slot_bytes[channel] / 4);
+    o.row_words = 0;
+    return o;
 }
 
 int xchg_world(const dc_xchg* x) { return x->world; }

@@ -31,6 +31,49 @@ struct XchgLL {
     unsigned long long timeout_ns;
 };
 
+// What a producer kernel needs to store its results straight into every rank's copy of a channel (fan-out fused
+// into the kernel that computes the values, instead of a copy kernel afterwards).  Word w of the logical block
+// (row r, word c of the row) lands at word index (r / rows_per_block) * block_stride + rank_off
+// + (r % rows_per_block) * row_words + c of the channel: one contiguous block per rank (rows_per_block = all
+// rows, rank_off = rank * slot words) or row groups interleaved by rank.
+struct XchgOut {
+    unsigned char* chan[kXchgMaxWorld];   // every rank's copy of the channel
+    int world;                            // 0: no fan-out (the kernel writes its ordinary outputs only)
+    int channel;
+    uint32_t* epoch;                      // this rank's epoch words
+    uint32_t* done;                       // CTA counter of the running exchange
+    int64_t rows_per_block, block_stride, rank_off, row_words;
+};
+
+__device__ __forceinline__ int64_t xchg_word_index(const XchgOut& o, int64_t row, int64_t col_word) {
+    return (row / o.rows_per_block) * o.block_stride + o.rank_off + (row % o.rows_per_block) * o.row_words + col_word;
+}
+// one {word, epoch} pair to every rank
+__device__ __forceinline__ void xchg_put(const XchgOut& o, uint32_t epoch, int64_t word, uint32_t value) {
+    for (int r = 0; r < o.world; r++) {
+        uint2* dst = reinterpret_cast<uint2*>(o.chan[r]) + word;
+        asm volatile("st.volatile.global.v2.u32 [%0], {%1,%2};\n" ::"l"(dst), "r"(value), "r"(epoch) : "memory");
+    }
+}
+// two pairs (words `word` and `word + 1`, word even) to every rank with one 16-byte store each
+__device__ __forceinline__ void xchg_put2(const XchgOut& o, uint32_t epoch, int64_t word, uint32_t v0, uint32_t v1) {
+    for (int r = 0; r < o.world; r++) {
+        uint4* dst = reinterpret_cast<uint4*>(o.chan[r]) + word / 2;
+        asm volatile("st.volatile.global.v4.u32 [%0], {%1,%2,%3,%4};\n" ::"l"(dst), "r"(v0), "r"(epoch), "r"(v1), "r"(epoch) : "memory");
+    }
+}
+// Epoch the stores of this kernel carry.  Every participating CTA reads it before it can call xchg_finish.
+__device__ __forceinline__ uint32_t xchg_next_epoch(const XchgOut& o) { return o.epoch[o.channel] + 1u; }
+// Called by all threads of every participating CTA after its last put: the CTA that finishes last advances
+// the channel's epoch word (read by later kernels of this rank's stream).
+__device__ __forceinline__ void xchg_finish(const XchgOut& o, uint32_t epoch, unsigned n_ctas) {
+    __syncthreads();
+    if (threadIdx.x == 0 && atomicAdd(o.done, 1u) == n_ctas - 1) {
+        *o.done = 0u;
+        o.epoch[o.channel] = epoch;
+    }
+}
+
 __device__ __forceinline__ uint4 ld_volatile16(const uint4* p) {
     uint4 v;
     asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
@@ -64,6 +107,7 @@ __device__ __forceinline__ uint2 xchg_poll(const uint4* p, uint32_t want, const 
 
 // host-side accessors used by the engine's sharded step
 XchgLL xchg_ll_args(const dc_xchg* x, int channel);
+XchgOut xchg_out_args(const dc_xchg* x, int channel);   // one block per rank; callers may change the layout fields
 int xchg_world(const dc_xchg* x);
 int xchg_rank(const dc_xchg* x);
 int64_t xchg_slot_bytes(const dc_xchg* x, int channel);

@@ -135,10 +135,12 @@ __global__ void __launch_bounds__(kSelThreads, 1)
 topk_select_kernel(const uint32_t* __restrict__ bits, const uint32_t* __restrict__ ids, int64_t in_stride, int64_t n,
                    const int32_t* __restrict__ n_dev, int k, const uint32_t* minmax, uint32_t* minmax_reset,
                    uint32_t id_offset, uint32_t* __restrict__ out_bits, uint32_t* __restrict__ out_ids,
-                   int64_t out_stride, int kpad, int raw_cap, uint32_t* __restrict__ status) {
+                   int64_t out_stride, int kpad, int raw_cap, uint32_t* __restrict__ status, const XchgOut xo) {
     pdl_launch_dependents();
     pdl_wait();
     if (n_dev != nullptr) n = min(n, static_cast<int64_t>(*n_dev));  // scores valid now (n is the launch's upper bound)
+    // sequence-sharded search: the sorted ranking keys also go straight into every rank's exchange buffer
+    const uint32_t xepoch = xo.world ? xchg_next_epoch(xo) : 0u;
     cg::cluster_group cluster = cg::this_cluster();
     const unsigned rank = cluster.block_rank();
     const unsigned csize = cluster.num_blocks();
@@ -575,7 +577,9 @@ topk_select_kernel(const uint32_t* __restrict__ bits, const uint32_t* __restrict
             if (out_bits) out_bits[prob * out_stride + target] = static_cast<uint32_t>(key >> 32);
             if (out_ids)
                 out_ids[prob * out_stride + target] = static_cast<uint32_t>(key & 0xFFFFFFFFull) + (live ? id_offset : 0u);
+            if (xo.world) xchg_put(xo, xepoch, xo.rank_off + prob * out_stride + target, static_cast<uint32_t>(key >> 32));
         }
+        if (xo.world) xchg_finish(xo, xepoch, gridDim.y);
         return;
     }
     if (!take_all && ctl.out_count != base_out && tid == 0) ctl.error = 3;
@@ -589,7 +593,9 @@ topk_select_kernel(const uint32_t* __restrict__ bits, const uint32_t* __restrict
         unsigned long long key = live ? s_out[i] : ~0ull;
         if (out_bits) out_bits[prob * out_stride + i] = static_cast<uint32_t>(key >> 32);
         if (out_ids) out_ids[prob * out_stride + i] = static_cast<uint32_t>(key & 0xFFFFFFFFull) + (live ? id_offset : 0u);
+        if (xo.world) xchg_put(xo, xepoch, xo.rank_off + prob * out_stride + i, static_cast<uint32_t>(key >> 32));
     }
+    if (xo.world) xchg_finish(xo, xepoch, gridDim.y);
 }
 
 int pow2_floor(int x) { int p = 1; while (p * 2 <= x) p *= 2; return p; }
@@ -715,9 +721,11 @@ int select_prepare() {
 // to (0xFFFFFFFF, 0) once it has read them, ready for the next scan's atomic min / max.
 // n: scores per problem the launch is sized for; n_dev (may be NULL): device word with the number that is
 // valid when the kernel runs (<= n).
+// xout (may be NULL): the sorted ranking keys are also stored, in pair format, into every rank's copy of an
+// exchange channel (problem p's list at word rank_off + p * out_stride).
 int topk_select(const uint32_t* bits, const uint32_t* ids, int64_t in_stride, int n_prob, int64_t n, int k,
                 const uint32_t* minmax, uint32_t id_offset, uint32_t* out_bits, uint32_t* out_ids, int64_t out_stride,
-                uint32_t* status, cudaStream_t stream, uint32_t* minmax_reset, const int32_t* n_dev) {
+                uint32_t* status, cudaStream_t stream, uint32_t* minmax_reset, const int32_t* n_dev, const XchgOut* xout) {
     DC_REQUIRE(bits != nullptr, "topk_select: null scores");
     DC_REQUIRE(k >= 0 && k <= DC_MAX_TOPK, "topk_select: k=%d outside [0, %d]", k, DC_MAX_TOPK);
     DC_REQUIRE(n >= 0 && n < (1ll << 32), "topk_select: n=%lld outside [0, 2^32)", static_cast<long long>(n));
@@ -739,10 +747,12 @@ int topk_select(const uint32_t* bits, const uint32_t* ids, int64_t in_stride, in
     while (by_work < 8 && static_cast<int64_t>(by_work) * 16384 < n) by_work <<= 1;
     csize = std::min(csize, by_work);
 
+    XchgOut xo = {};
+    if (xout != nullptr) xo = *xout;
     DC_CUDA_TRY(launch_chained(topk_select_kernel, dim3(static_cast<unsigned>(csize), static_cast<unsigned>(n_prob), 1),
                                dim3(kSelThreads, 1, 1), smem, stream, static_cast<unsigned>(csize), bits, ids, in_stride, n,
                                n_dev, k, minmax, minmax_reset, id_offset, out_bits, out_ids, out_stride, kpad, raw_cap,
-                               status));
+                               status, xo));
     return DC_OK;
 }
 

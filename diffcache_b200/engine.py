@@ -294,6 +294,12 @@ class DiffCacheGPU:
                                                       _ptr(out), _ptr(out_idx), _ptr(out_lse), _current_stream(stream)))
         self._count_query()
 
+    def set_output_exchange(self, exchange, channel: int = 0) -> None:
+        """Head-sharded layers: every following ``decode_attend*`` call also stores its output slice into every
+        rank's copy of ``channel`` of ``exchange`` (a :class:`diffcache_b200.sharded.PeerExchange`; ``None``
+        switches it off), interleaved so that the channel reads ``(bsz, world, q_head_num * head_dim)``."""
+        _lib.check(self._lib.dc_set_output_exchange(self._h, None if exchange is None else exchange._h, int(channel)))
+
     def window_push(self, k_new, v_new, res_k, res_v, window_state, stream=None) -> None:
         """Append the step's new token to this layer's window ring (see ``dc_window_push``): the oldest
         token is spilled into the scanned store once the window is full.  ``window_state`` is the int32

@@ -118,21 +118,23 @@ class AttentionStack:
             q = qkv[:, :nq].unflatten(1, (self.q_local, D))
             kn = qkv[:, nq:nq + nkv].unflatten(1, (self.kv_local, D))
             vn = qkv[:, nq + nkv:].unflatten(1, (self.kv_local, D))
+            ch = layer % self.xchg_channels if self.xchg is not None else -1
+            if self.xchg is not None and ch == self._last_channel:
+                # two exchanges in a row on one channel (a call that stopped after an odd number of layers):
+                # make sure every rank has finished reading the block this one overwrites
+                if torch.cuda.is_current_stream_capturing():
+                    raise RuntimeError("consecutive exchanges on one channel cannot be captured")
+                torch.cuda.synchronize(self.device)
+                dist.barrier(self.pg)
+            self._last_channel = ch
+            self.engines[layer].set_output_exchange(self.xchg if self.xchg is not None else None, max(ch, 0))
+            # with the peer exchange the step's last kernel also stores the slice into every rank's buffer,
+            # where it lands as (B, world, q_local*D)
             self.engines[layer].decode_attend(q, self.attn_local, self.topk, res_k=self.res_k[layer],
                                               res_v=self.res_v[layer], res_len=self.res_rows, k_new=kn, v_new=vn)
             if probe is not None and layer == 0:
                 probe.update(q=q.clone(), k_new=kn.clone(), v_new=vn.clone(), attn=self.attn_local.clone())
             if self.xchg is not None:
-                ch = layer % self.xchg_channels
-                if ch == self._last_channel:
-                    # two pushes in a row on one channel (a call that stopped after an odd number of layers):
-                    # make sure every rank has finished reading the block this push overwrites
-                    if torch.cuda.is_current_stream_capturing():
-                        raise RuntimeError("consecutive pushes on one exchange channel cannot be captured")
-                    torch.cuda.synchronize(self.device)
-                    dist.barrier(self.pg)
-                self._last_channel = ch
-                self.xchg.push_rows(ch, self.attn_local.view(B, -1))   # lands as (B, world, q_local*D) on every rank
                 attn = self.xchg_views[ch]
                 self.xchg.collect(ch, attn)                           # waits for all slices, unpacks them densely
             elif self.world > 1:

@@ -360,6 +360,16 @@ int dc_xchg_check(dc_xchg* x, uint64_t stream);
  * smaller global row id: nsw.rs:74-91,612).
  */
 int dc_sharded_slot_bytes(dc_engine* e, int topk, int64_t* out2);
+/*
+ * Head-sharded layers (every rank holds some kv heads of a layer and needs all ranks' attention outputs for
+ * the output projection): after dc_set_output_exchange(e, x, channel) every dc_decode_attend* call of this
+ * engine also stores its (bsz, q_heads, head_dim) output into every rank's copy of the channel, interleaved so
+ * that the channel holds (bsz, world, q_heads * head_dim) — the stores are part of the kernel that produces
+ * the output.  The consumer gets it with dc_xchg_collect.  The channel's slot must be bsz * q_heads * head_dim
+ * * 2 bytes; x = NULL switches it off.  Consecutive exchanges must use different channels (one per layer,
+ * round-robin) unless something else orders the ranks between them.
+ */
+int dc_set_output_exchange(dc_engine* e, dc_xchg* x, int channel);
 int dc_sharded_local(dc_engine* e, dc_xchg* x, const void* q, int topk, uint64_t stream);
 int dc_sharded_attend(dc_engine* e, dc_xchg* x, const void* q, const void* k_new, const void* v_new, void* res_k,
                       void* res_v, int64_t res_stride_b, int64_t res_stride_h, int res_len, float scale, uint64_t stream);

@@ -16,9 +16,11 @@
 //   * one elected thread issues eight tcgen05.mma (K = 16 each) per tile and commits them to two
 //     mbarriers: "stage free" for the TMA producer and "accumulator ready" for the epilogue;
 //   * four epilogue warps read column 0 of the accumulator (tcgen05.ld 32x32b: lane = key row), turn it
-//     into the ranking key bits(65536 - dot) and write 128 consecutive keys per tile; eight accumulators
-//     rotate, so the MMAs of the next tiles are issued while earlier tiles are still being read out (with
-//     two, the MMA -> commit -> read-out -> release round trip limited the kernel to 4.9 TB/s).
+//     into the ranking key bits(65536 - dot) and write 128 consecutive keys per tile.  Accumulators are handed
+//     over in pairs (two tiles per barrier round trip), four pairs rotate, and two groups of four epilogue warps
+//     take alternate pairs: with one group reading one tile per round trip, the read-out (barrier wake-up,
+//     tcgen05.ld, release) took about 1 us per tile and held the kernel at 4.9 TB/s whatever the number of
+//     accumulators.
 // Persistent CTAs (one per SM) each take a contiguous range of tiles.  Every mbarrier wait is bounded: a
 // wait that runs out records 211..215 in the status word, the roles drain, tensor memory is freed and
 // the kernel returns.  No multicast, one CTA per cluster.
@@ -36,15 +38,15 @@ namespace dc {
 
 namespace {
 
-constexpr int kTcThreads = 256;
+constexpr int kTcThreads = 384;                      // producer, MMA, allocator, query warps + two groups of 4 epilogue warps
 constexpr int kTcStages = 5;
 constexpr int kTileRows = 128;
 constexpr int kTileDim = 128;
 constexpr int kHalfBytes = kTileRows * 128;          // one 64-column box: 128 rows x 128 bytes
 constexpr int kStageBytes = 2 * kHalfBytes;          // 32 KB
 constexpr int kQTileBytes = 2 * 16 * 128;            // 16 rows x 128 dims, two 64-column halves
-constexpr int kAcc = 8;                              // accumulators in flight (tile i+1.. multiply while tile i is read)
-constexpr int kTmemCols = kAcc * 16;                 // 16 fp32 columns each; a power of two >= 32
+constexpr int kPairs = 4;                            // accumulator pairs in flight: a pair = two tiles, read out together
+constexpr int kTmemCols = kPairs * 32;               // 16 fp32 columns per tile; a power of two >= 32
 constexpr int kTcSmemBytes = kTcStages * kStageBytes + 2 * kQTileBytes + 1024;
 
 __device__ __forceinline__ void mbar_arrive_plain(unsigned long long* bar) {
@@ -87,7 +89,7 @@ __host__ __device__ constexpr uint32_t instr_desc(int fmt) {
 
 struct TcShared {
     unsigned long long full[kTcStages], empty[kTcStages];
-    unsigned long long acc_full[kAcc], acc_empty[kAcc];
+    unsigned long long acc_full[kPairs], acc_empty[kPairs];
     unsigned long long q_full[2], q_empty[2];
     uint32_t tmem_base;
     uint32_t s_lo, s_hi;
@@ -117,7 +119,7 @@ score_scan_tc_kernel(const __grid_constant__ CUtensorMap kmap, int64_t rows_per_
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kTcStages; s++) { mbar_init(&sh.full[s], 1); mbar_init(&sh.empty[s], 1); }
-        for (int a = 0; a < kAcc; a++) { mbar_init(&sh.acc_full[a], 1); mbar_init(&sh.acc_empty[a], 4); }
+        for (int a = 0; a < kPairs; a++) { mbar_init(&sh.acc_full[a], 1); mbar_init(&sh.acc_empty[a], 4); }
         for (int a = 0; a < 2; a++) { mbar_init(&sh.q_full[a], 1); mbar_init(&sh.q_empty[a], 1); }
         mbar_init_fence();
     }
@@ -157,7 +159,9 @@ score_scan_tc_kernel(const __grid_constant__ CUtensorMap kmap, int64_t rows_per_
             constexpr uint32_t idesc = instr_desc(DT == DC_BF16 ? 1 : 0);
             int64_t cur_p = -1, prob_ord = -1;
             for (int64_t i = 0; i < my_tiles; i++) {
-                const int s = static_cast<int>(i % kTcStages), a = static_cast<int>(i % kAcc);
+                const int s = static_cast<int>(i % kTcStages);
+                const int64_t pair = i / 2;                       // tiles 2*pair and 2*pair+1 share a read-out
+                const int a = static_cast<int>(pair % kPairs);
                 const int64_t t = t_begin + i, p = t / tiles_per_prob;
                 bool ok = true;
                 if (p != cur_p) {   // first tile of a problem in this CTA: its query tile must be ready
@@ -165,8 +169,8 @@ score_scan_tc_kernel(const __grid_constant__ CUtensorMap kmap, int64_t rows_per_
                     ok = mbar_wait_bounded(&sh.q_full[prob_ord & 1], static_cast<unsigned>((prob_ord >> 1) & 1));
                     if (!ok && status) atomicMax(status, 212u);
                 }
-                if (ok && i >= kAcc) {
-                    ok = mbar_wait_bounded(&sh.acc_empty[a], static_cast<unsigned>((i / kAcc - 1) & 1));
+                if (ok && (i & 1) == 0 && pair >= kPairs) {
+                    ok = mbar_wait_bounded(&sh.acc_empty[a], static_cast<unsigned>((pair / kPairs - 1) & 1));
                     if (!ok && status) atomicMax(status, 213u);
                 }
                 if (ok) {
@@ -182,10 +186,10 @@ score_scan_tc_kernel(const __grid_constant__ CUtensorMap kmap, int64_t rows_per_
                     // k-step k covers dims [16k, 16k+16): half k/4 of the tile, 32 bytes into its 128-byte rows
                     const uint64_t ad = smem_desc_sw128(a_base + (k / 4) * kHalfBytes + (k % 4) * 32);
                     const uint64_t bd = smem_desc_sw128(b_base + (k / 4) * (kQTileBytes / 2) + (k % 4) * 32);
-                    tc_mma_f16(tmem + static_cast<uint32_t>(a * 16), ad, bd, idesc, k > 0 ? 1u : 0u);
+                    tc_mma_f16(tmem + static_cast<uint32_t>(a * 32 + (i & 1) * 16), ad, bd, idesc, k > 0 ? 1u : 0u);
                 }
                 tc_commit(&sh.empty[s]);       // the stage may be refilled once these MMAs have read it
-                tc_commit(&sh.acc_full[a]);    // ... and the accumulator is complete
+                if ((i & 1) == 1 || i + 1 == my_tiles) tc_commit(&sh.acc_full[a]);    // ... and the pair is complete
                 const bool last_of_prob = (i + 1 == my_tiles) || ((t + 1) / tiles_per_prob != p);
                 if (last_of_prob) tc_commit(&sh.q_empty[prob_ord & 1]);
             }
@@ -218,8 +222,10 @@ score_scan_tc_kernel(const __grid_constant__ CUtensorMap kmap, int64_t rows_per_
             if (lane == 0) mbar_arrive_plain(&sh.q_full[buf]);
         }
     } else if (warp >= 4) {
-        // ---- epilogue: warp w reads tensor-memory lanes [32 (w % 4), +32) = key rows of the tile ----
+        // ---- epilogue: two groups of four warps take alternate accumulator pairs; warp w reads tensor-memory
+        // lanes [32 (w % 4), +32) = key rows of the tile ----
         const int quarter = warp & 3;
+        const int group_id = (warp - 4) >> 2;
         uint32_t lo = 0xFFFFFFFFu, hi = 0u;
         int64_t cur_p = -1;
         auto flush_minmax = [&]() {
@@ -231,31 +237,38 @@ score_scan_tc_kernel(const __grid_constant__ CUtensorMap kmap, int64_t rows_per_
             }
             lo = 0xFFFFFFFFu; hi = 0u;
         };
-        for (int64_t i = 0; i < my_tiles; i++) {
-            const int a = static_cast<int>(i % kAcc);
-            const int64_t t = t_begin + i, p = t / tiles_per_prob, r0 = (t % tiles_per_prob) * kTileRows;
-            if (p != cur_p) {
-                if (cur_p >= 0) flush_minmax();
-                cur_p = p;
-            }
-            if (!__all_sync(0xFFFFFFFFu, mbar_wait_bounded(&sh.acc_full[a], static_cast<unsigned>((i / kAcc) & 1)))) {
+        const int64_t n_pairs = (my_tiles + 1) / 2;
+        for (int64_t pair = group_id; pair < n_pairs; pair += 2) {
+            const int a = static_cast<int>(pair % kPairs);
+            if (!__all_sync(0xFFFFFFFFu, mbar_wait_bounded(&sh.acc_full[a], static_cast<unsigned>((pair / kPairs) & 1)))) {
                 if (lane == 0 && status) atomicMax(status, 216u);
                 break;
             }
             tc_fence_after();
-            uint32_t v;
-            const uint32_t taddr = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(a * 16);
-            asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];\n" : "=r"(v) : "r"(taddr) : "memory");
+            const bool two = 2 * pair + 1 < my_tiles;
+            uint32_t v[2] = {0u, 0u};
+            const uint32_t taddr = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(a * 32);
+            asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];\n" : "=r"(v[0]) : "r"(taddr) : "memory");
+            if (two) asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];\n" : "=r"(v[1]) : "r"(taddr + 16u) : "memory");
             asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive_plain(&sh.acc_empty[a]);   // the accumulator may be overwritten
-            const int64_t r = r0 + quarter * 32 + lane;
-            if (r < n) {
-                const uint32_t b = dist_bits(__uint_as_float(v));
-                scores[p * score_stride + r] = b;
-                lo = min(lo, b);
-                hi = max(hi, b);
+            if (lane == 0) mbar_arrive_plain(&sh.acc_empty[a]);   // the pair may be overwritten
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                if (h == 1 && !two) break;
+                const int64_t t = t_begin + 2 * pair + h, p = t / tiles_per_prob, r0 = (t % tiles_per_prob) * kTileRows;
+                if (p != cur_p) {
+                    if (cur_p >= 0) flush_minmax();
+                    cur_p = p;
+                }
+                const int64_t r = r0 + quarter * 32 + lane;
+                if (r < n) {
+                    const uint32_t b = dist_bits(__uint_as_float(v[h]));
+                    scores[p * score_stride + r] = b;
+                    lo = min(lo, b);
+                    hi = max(hi, b);
+                }
             }
         }
         if (cur_p >= 0) flush_minmax();

@@ -34,6 +34,21 @@ constexpr int kSegMax = 512;    // longest first-pass bin the in-place segment o
 constexpr int kSelUnroll = 4;   // independent loads in flight per thread
 constexpr int kMaxPasses = 8;  // 64 key bits / 12 bits per pass = 6 passes at most
 
+// Phase marks for tuning (compiled in only with -DDC_SEL_MARKS): the leader CTA of problem 0 stores the global
+// timer at phase boundaries into the words behind the status word.
+#ifdef DC_SEL_MARKS
+#define DC_MARK(i)                                                                                          \
+    do {                                                                                                    \
+        if (status != nullptr && blockIdx.y == 0 && cluster.block_rank() == 0 && threadIdx.x == 0) {        \
+            unsigned long long _t;                                                                          \
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(_t));                                         \
+            reinterpret_cast<unsigned long long*>(status)[2 + (i)] = _t;                                    \
+        }                                                                                                   \
+    } while (0)
+#else
+#define DC_MARK(i) do {} while (0)
+#endif
+
 struct SelCtl {
     unsigned long long lo, hi;
     uint32_t need;        // how many keys are still to be taken from [lo, hi]
@@ -142,6 +157,7 @@ topk_select_kernel(const uint32_t* __restrict__ bits, const uint32_t* __restrict
     // sequence-sharded search: the sorted ranking keys also go straight into every rank's exchange buffer
     const uint32_t xepoch = xo.world ? xchg_next_epoch(xo) : 0u;
     cg::cluster_group cluster = cg::this_cluster();
+    DC_MARK(0);
     const unsigned rank = cluster.block_rank();
     const unsigned csize = cluster.num_blocks();
     const int64_t prob = blockIdx.y;
@@ -389,6 +405,7 @@ topk_select_kernel(const uint32_t* __restrict__ bits, const uint32_t* __restrict
             }
         }
 
+        DC_MARK(1);
         // ---- narrowing passes ----
         for (int pass = 0; pass < kMaxPasses && !listed; pass++) {
             const unsigned long long range = hi - lo;
@@ -420,6 +437,7 @@ topk_select_kernel(const uint32_t* __restrict__ bits, const uint32_t* __restrict
                 });
             }
             __syncthreads();
+            DC_MARK(2);
             if (rank != 0) {
                 for (int b = tid; b < kBins; b += kSelThreads) {
                     uint32_t c = s_hist[b];
@@ -427,6 +445,7 @@ topk_select_kernel(const uint32_t* __restrict__ bits, const uint32_t* __restrict
                 }
             }
             cluster.sync();  // merged histogram complete in the leader
+            DC_MARK(3);
 
             if (rank == 0) leader_find_threshold(pass == 0);
             cluster.sync();  // ctl published
@@ -443,6 +462,7 @@ topk_select_kernel(const uint32_t* __restrict__ bits, const uint32_t* __restrict
 
     // ---- final pass: emit keys below lo, collect the threshold bin ----
     cluster.sync();  // leader's counters are initialised / nobody still reads ctl.t
+    DC_MARK(4);
     const uint32_t base_out = static_cast<uint32_t>(k_eff) - need;  // keys strictly below lo
     const bool single_value = (lo == hi);
     // One narrowing pass on the dist bits (the normal case): every winner below the threshold bin
@@ -503,6 +523,7 @@ topk_select_kernel(const uint32_t* __restrict__ bits, const uint32_t* __restrict
                 }
             });
             __syncthreads();
+            DC_MARK(5);
             const uint32_t cnt = ctl.raw_count;
             if (cnt <= static_cast<uint32_t>(raw_cap)) {   // (a slice with more keys than fit is placed directly below)
                 for (uint32_t r = tid; r < cnt; r += kSelThreads) place_key(s_raw[r]);
@@ -517,6 +538,7 @@ topk_select_kernel(const uint32_t* __restrict__ bits, const uint32_t* __restrict
         }
     }
     cluster.sync();  // all remote writes into the leader have landed
+    DC_MARK(6);
     if (rank != 0) return;
     // every CTA read the key range long ago: hand the pair back in the state the next scan folds into
     if (minmax_reset != nullptr && tid == 0) { minmax_reset[2 * prob] = 0xFFFFFFFFu; minmax_reset[2 * prob + 1] = 0u; }
@@ -552,6 +574,7 @@ topk_select_kernel(const uint32_t* __restrict__ bits, const uint32_t* __restrict
         }
     }
     __syncthreads();
+    DC_MARK(7);
     if (bucket) {
         // The threshold-bin winners are already ordered at [base_out, k_eff).  Order the rest: the
         // rank of a key inside its (short) segment is the number of smaller keys there, and the
@@ -580,6 +603,8 @@ topk_select_kernel(const uint32_t* __restrict__ bits, const uint32_t* __restrict
             if (xo.world) xchg_put(xo, xepoch, xo.rank_off + prob * out_stride + target, static_cast<uint32_t>(key >> 32));
         }
         if (xo.world) xchg_finish(xo, xepoch, gridDim.y);
+        __syncthreads();
+        DC_MARK(8);
         return;
     }
     if (!take_all && ctl.out_count != base_out && tid == 0) ctl.error = 3;

@@ -55,7 +55,37 @@ pq_adc_scan_kernel(const uint8_t* __restrict__ codes, int64_t prob_stride, int64
     const int64_t row0 = static_cast<int64_t>(blockIdx.x) * rows_per_cta;
     const int64_t row_end = min(n, row0 + rows_per_cta);
     uint32_t lo = 0xFFFFFFFFu, hi = 0u;
-    for (int64_t r = row0 + threadIdx.x; r < row_end; r += kAdcThreads) {
+    int64_t r_first = row0 + threadIdx.x;
+    if (M == 16) {
+        // Four rows per thread and iteration: four 16-byte loads in flight, and the 64 table lookups of the four
+        // rows interleave, so the shared-memory latency of one row's chain is hidden by the others.  Each row is
+        // still summed in subspace order.
+        constexpr int U = 4;
+        for (; r_first + (U - 1) * kAdcThreads < row_end; r_first += U * kAdcThreads) {
+            uint4 w[U];
+#pragma unroll
+            for (int u = 0; u < U; u++) w[u] = ld_stream16(cp + (r_first + u * kAdcThreads) * M);
+            float acc[U];
+#pragma unroll
+            for (int u = 0; u < U; u++) acc[u] = 0.0f;
+#pragma unroll
+            for (int j = 0; j < 16; j++) {
+#pragma unroll
+                for (int u = 0; u < U; u++) {
+                    const uint32_t word = j < 4 ? w[u].x : j < 8 ? w[u].y : j < 12 ? w[u].z : w[u].w;
+                    acc[u] += s_lut[j * 256 + ((word >> (8 * (j % 4))) & 0xFFu)];
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < U; u++) {
+                const uint32_t b = dist_bits(acc[u]);
+                sp[r_first + u * kAdcThreads] = b;
+                lo = min(lo, b);
+                hi = max(hi, b);
+            }
+        }
+    }
+    for (int64_t r = r_first; r < row_end; r += kAdcThreads) {
         float s = 0.0f;
         if (M % 16 == 0) {
 #pragma unroll

@@ -17,6 +17,7 @@
 #include <cooperative_groups.h>
 
 #include <algorithm>
+#include <cstdlib>
 
 #include "exchange.cuh"
 
@@ -766,8 +767,13 @@ int topk_select(const uint32_t* bits, const uint32_t* ids, int64_t in_stride, in
 
     // Enough CTAs per problem to occupy the SMs, at most the portable cluster size of 8,
     // and no more than one CTA per 16K keys.
+    static const int max_cluster = [] {   // DC_SELECT_MAX_CLUSTER: 1, 2, 4 or 8 (default) CTAs per problem at most
+        const char* v = std::getenv("DC_SELECT_MAX_CLUSTER");
+        const int c = (v != nullptr && *v) ? std::atoi(v) : 8;
+        return c >= 8 ? 8 : c >= 4 ? 4 : c >= 2 ? 2 : 1;
+    }();
     int csize = pow2_floor(std::max(1, sm_count() / std::max(1, n_prob)));
-    csize = std::min(csize, 8);
+    csize = std::min(csize, max_cluster);
     int by_work = 1;
     while (by_work < 8 && static_cast<int64_t>(by_work) * 16384 < n) by_work <<= 1;
     csize = std::min(csize, by_work);

@@ -170,7 +170,10 @@ int dc_update_r_sq(dc_engine* e, const float* r_sq, int n);
  *  topk     clamped to ctx_len; 0 skips retrieval.
  *  scale    softmax scale; <= 0 selects head_dim^-0.5 (flash-attn default).
  *  out      (bsz, q_heads, head_dim) device, engine dtype.
- *  out_idx  optional (bsz, kv_heads, topk) int32 selected rows, best first.
+ *  out_idx  optional (bsz, kv_heads, k) int32 selected rows, best first, k = min(topk, rows), where rows is
+ *           ctx_len — or max_ctx_len when the call is being captured into a CUDA graph or follows
+ *           dc_window_push (the launches are then sized for the whole store; entries beyond the rows the
+ *           store holds are 0xFFFFFFFF).
  *  out_lse  optional (bsz, q_heads) fp32 natural-log sum-exp of scaled scores.
  */
 int dc_decode_attend(dc_engine* e, const void* q, const void* k_new, const void* v_new,
@@ -354,8 +357,9 @@ int dc_xchg_check(dc_xchg* x, uint64_t stream);
  *                       resident rows / new token as given there) and pushes the partial result;
  *   dc_sharded_combine  waits for all ranks' partials and merges them by log-sum-exp into `out`
  *                       (bsz, q_heads, head_dim), identical on every rank.
- * dc_sharded_decode_attend runs the three in a row: the whole step is one call and eight kernels on
- * `stream` (topk must be even), capturable in a CUDA graph once the first call has allocated the per-engine buffers.
+ * dc_sharded_decode_attend runs the three in a row: the whole step is one call and six kernels on
+ * `stream` (scan; select, which also stores the keys into every rank's buffer; prefix count; attention;
+ * split merge, which also stores the partials into every rank's buffer; final merge; topk must be even), capturable in a CUDA graph once the first call has allocated the per-engine buffers.
  * Results are those of dc_decode_attend on the concatenated rows (same ranking keys, ties to the
  * smaller global row id: nsw.rs:74-91,612).
  */

@@ -884,6 +884,23 @@ def run_cfg0(cfg, ranks: Ranks, steps, warmup):
     for _ in range(max(warmup, 4)):
         step()
     per = float(np.median(timed_loops(step, steps, 3, ranks)))
+    # per-kernel times of the stream-launched step (CUDA events after every phase switch the overlap of
+    # consecutive kernels off, so their sum exceeds the step)
+    for st in sets:
+        st[0].set_phase_timing(steps)
+    for _ in range(4 * min(steps, 25)):
+        step()
+    torch.cuda.synchronize(device)
+    tot = {"scan": 0.0, "select": 0.0, "attend": 0.0}
+    n_rec = 0
+    for st in sets:
+        ph = st[0].phase_times()
+        st[0].set_phase_timing(0)
+        n_rec += ph["steps"]
+        tot["scan"] += ph["scan_ms"]
+        tot["select"] += ph["select_ms"]
+        tot["attend"] += ph["attend_ms"]
+    phases_us = {k: round(1e3 * v / max(1, n_rec), 2) for k, v in tot.items()}
 
     def four():
         for _ in range(4):
@@ -900,6 +917,7 @@ def run_cfg0(cfg, ranks: Ranks, steps, warmup):
         st[0].close()
     best = min(per, graph_per) if graph_per else per
     return {"value": 1e3 / best, "ms_per_step": best, "ms_per_step_stream_launch": per, "ms_per_step_cuda_graph": graph_per,
+            "phases_us": phases_us,
             "l2_policy": "4 input sets rotated (each 134 MB of K+V, total 537 MB > L2)", "gpu_launches_per_step": 4}
 
 

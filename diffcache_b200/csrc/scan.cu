@@ -41,8 +41,9 @@ score_scan_kernel(const uint16_t* __restrict__ keys, int64_t prob_stride, int64_
                   uint32_t* __restrict__ scores, int64_t score_stride, uint32_t* __restrict__ minmax, int rows_per_cta) {
     pdl_launch_dependents();
     pdl_wait();
-    if (n_dev != nullptr) n = *n_dev;   // rows valid now (the grid was sized for an upper bound)
-    if (static_cast<int64_t>(blockIdx.x) * rows_per_cta >= n) return;
+    // rows valid now (the grid was sized for an upper bound); the load is issued together with the query loads
+    // below so that their latencies overlap, and only then decides whether this CTA has rows at all
+    const int64_t n_now = n_dev != nullptr ? static_cast<int64_t>(*n_dev) : n;
     constexpr int D = LPR * 8;
     constexpr int R = 32 / LPR;               // rows covered by one warp-wide load
     constexpr int TR = kLoadsPerTile * R;     // rows per warp tile
@@ -54,6 +55,8 @@ score_scan_kernel(const uint16_t* __restrict__ keys, int64_t prob_stride, int64_
 
     float qv[8];
     load_query8<DT>(query_base(q, prob, D, q_mode, group, kv_heads, q_stride_b), D, q_mode, group, col * 8, qv);
+    n = n_now;
+    if (static_cast<int64_t>(blockIdx.x) * rows_per_cta >= n) return;
 
     const uint16_t* kp = keys + prob * prob_stride + col * 8;
     uint32_t* sp = scores + prob * score_stride;
@@ -123,8 +126,9 @@ score_scan_wide_kernel(const uint16_t* __restrict__ keys, int64_t prob_stride, i
                        uint32_t* __restrict__ minmax, int rows_per_cta) {
     pdl_launch_dependents();
     pdl_wait();
-    if (n_dev != nullptr) n = *n_dev;   // rows valid now (the grid was sized for an upper bound)
-    if (static_cast<int64_t>(blockIdx.x) * rows_per_cta >= n) return;
+    // rows valid now (the grid was sized for an upper bound); the load is issued together with the query loads
+    // below so that their latencies overlap, and only then decides whether this CTA has rows at all
+    const int64_t n_now = n_dev != nullptr ? static_cast<int64_t>(*n_dev) : n;
     constexpr int D = LW * 16;
     constexpr int R = 32 / LW;
     constexpr int TR = kLoadsPerTile * R;
@@ -143,6 +147,8 @@ score_scan_wide_kernel(const uint16_t* __restrict__ keys, int64_t prob_stride, i
 #pragma unroll
         for (int j = 0; j < 8; j++) { qv[j] = a[j]; qv[8 + j] = b[j]; }
     }
+    n = n_now;
+    if (static_cast<int64_t>(blockIdx.x) * rows_per_cta >= n) return;
     const uint16_t* kp = keys + prob * prob_stride + col * 16;
     uint32_t* sp = scores + prob * score_stride;
     const int64_t row0 = static_cast<int64_t>(blockIdx.x) * rows_per_cta;

@@ -142,7 +142,7 @@ class AttentionStack:
                 attn = self.attn_full.view(self.world, B, self.kv_local, -1).permute(1, 0, 2, 3).reshape(B, -1)
             else:
                 attn = self.attn_local.view(B, -1)
-            x = x + F.linear(attn, self.wo[layer])
+            x = torch.addmm(x, attn, self.wo[layer].t())   # residual + output projection in one GEMM epilogue
         return x
 
     def close(self) -> None:

@@ -458,13 +458,32 @@ lse_combine_kernel(const float* __restrict__ part_acc, int64_t acc_ps, int64_t a
         const unsigned long long t0 = global_timer_ns();
         bool fail = false;
         const int per = dim / 2 + 1;      // pair vectors per part: dim / 2 of accumulators, one of (m, l)
-        for (int i = tid; i < n_part * per; i += kCombineThreads) {
-            const int s = i / per, v = i % per;
-            const int64_t word = v < dim / 2 ? row * dim + 2 * v : ll_ml_off + row * 2;
-            const uint2 d = xchg_poll(ll.chan + s * ll.slot_vecs + word / 2, want, ll, t0, fail);
-            float* dst = s_stage + s * row_stride + (v < dim / 2 ? 2 * v : dim);
-            dst[0] = __uint_as_float(d.x);
-            dst[1] = __uint_as_float(d.y);
+        // four vectors per thread are loaded before the first is examined (one round trip for all of them);
+        // only vectors that have not arrived yet are polled one by one
+        const int total = n_part * per;
+        for (int i0 = tid; i0 < total; i0 += 4 * kCombineThreads) {
+            uint4 w[4];
+            const uint4* src[4];
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const int i = i0 + j * kCombineThreads;
+                if (i >= total) continue;
+                const int s = i / per, v = i % per;
+                const int64_t word = v < dim / 2 ? row * dim + 2 * v : ll_ml_off + row * 2;
+                src[j] = ll.chan + s * ll.slot_vecs + word / 2;
+                w[j] = ld_volatile16(src[j]);
+            }
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const int i = i0 + j * kCombineThreads;
+                if (i >= total) continue;
+                const int s = i / per, v = i % per;
+                uint2 d = make_uint2(w[j].x, w[j].z);
+                if (w[j].y != want || w[j].w != want) d = xchg_poll(src[j], want, ll, t0, fail);
+                float* dst = s_stage + s * row_stride + (v < dim / 2 ? 2 * v : dim);
+                dst[0] = __uint_as_float(d.x);
+                dst[1] = __uint_as_float(d.y);
+            }
         }
         __syncthreads();
         acc = s_stage; acc_ps = row_stride;

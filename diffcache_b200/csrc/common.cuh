@@ -71,7 +71,9 @@ struct PerDeviceOnce {
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
 
-bool pdl_enabled();  // false when the environment variable DC_PDL is "0"
+// Whether a launch on `stream` gets the attribute: not while the stream is being captured into a graph
+// (see the definition), never when the environment variable DC_PDL is "0".
+bool pdl_enabled(cudaStream_t stream);
 
 // cudaLaunchKernelEx with the programmatic-serialization attribute (and a cluster size when cluster_x > 0).
 template <class... KArgs, class... Args>
@@ -84,7 +86,7 @@ inline cudaError_t launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 bloc
     cfg.stream = stream;
     cudaLaunchAttribute attr[2];
     unsigned n_attr = 0;
-    if (pdl_enabled()) {
+    if (pdl_enabled(stream)) {
         attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
         attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
         n_attr++;

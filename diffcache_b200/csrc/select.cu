@@ -650,13 +650,25 @@ merge_sorted_count_kernel(const uint32_t* __restrict__ bits_all, int64_t rank_st
         const uint32_t want = ll.epoch[ll.channel];
         const unsigned long long t0 = global_timer_ns();
         bool fail = false;
-        for (int r = 0; r < world; r++) {
-            const uint4* src = ll.chan + r * ll.slot_vecs + (static_cast<int64_t>(p) * k) / 2;
-            uint32_t* dst = s_lists + static_cast<size_t>(r) * k;
-            for (int v = tid; v < k / 2; v += kMergeThreads) {
-                const uint2 d = xchg_poll(src + v, want, ll, t0, fail);
-                dst[2 * v] = d.x;
-                dst[2 * v + 1] = d.y;
+        // the loads of up to eight ranks' vectors are issued before the first is examined, so a thread pays
+        // one round trip per batch; only vectors that have not arrived yet are polled one by one
+        const int64_t base = (static_cast<int64_t>(p) * k) / 2;
+        for (int v = tid; v < k / 2; v += kMergeThreads) {
+            for (int r0 = 0; r0 < world; r0 += 8) {
+                uint4 w[8];
+#pragma unroll
+                for (int j = 0; j < 8; j++)
+                    if (r0 + j < world) w[j] = ld_volatile16(ll.chan + (r0 + j) * ll.slot_vecs + base + v);
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                    if (r0 + j >= world) continue;
+                    uint2 d = make_uint2(w[j].x, w[j].z);
+                    if (w[j].y != want || w[j].w != want)
+                        d = xchg_poll(ll.chan + (r0 + j) * ll.slot_vecs + base + v, want, ll, t0, fail);
+                    uint32_t* dst = s_lists + static_cast<size_t>(r0 + j) * k;
+                    dst[2 * v] = d.x;
+                    dst[2 * v + 1] = d.y;
+                }
             }
         }
     } else
@@ -677,6 +689,7 @@ merge_sorted_count_kernel(const uint32_t* __restrict__ bits_all, int64_t rank_st
         const uint32_t b = mine[i];
         if (b == 0xFFFFFFFFu) continue;  // pad: this rank holds fewer than k rows
         uint32_t rank = static_cast<uint32_t>(i);
+        // stops at the first list that pushes the key out of the best k (most keys beyond the first k / world)
         for (int r = 0; r < world && rank < static_cast<uint32_t>(k); r++) {
             if (r == my_rank) continue;
             const uint32_t* list = s_lists + static_cast<size_t>(r) * k;

@@ -778,8 +778,9 @@ int topk_select(const uint32_t* bits, const uint32_t* ids, int64_t in_stride, in
     if (smem + static_cast<size_t>(raw_cap) * 8 > 200 * 1024) raw_cap = 0;
     smem += static_cast<size_t>(raw_cap) * 8;
 
-    // Enough CTAs per problem to occupy the SMs, at most the portable cluster size of 8,
-    // and no more than one CTA per 16K keys.
+    // Enough CTAs per problem to occupy the SMs, at most the portable cluster size of 8, and no more than one
+    // CTA per 8K keys (measured on 8 problems x 32 448 keys, k = 1024: 14.8 us with one CTA per 16K keys, 13.0
+    // with one per 8K, 13.7 with one per 4K; a cluster of 16 CTAs was slower wherever it applied).
     static const int max_cluster = [] {   // DC_SELECT_MAX_CLUSTER: 1, 2, 4 or 8 (default) CTAs per problem at most
         const char* v = std::getenv("DC_SELECT_MAX_CLUSTER");
         const int c = (v != nullptr && *v) ? std::atoi(v) : 8;
@@ -788,7 +789,7 @@ int topk_select(const uint32_t* bits, const uint32_t* ids, int64_t in_stride, in
     int csize = pow2_floor(std::max(1, sm_count() / std::max(1, n_prob)));
     csize = std::min(csize, max_cluster);
     int by_work = 1;
-    while (by_work < 8 && static_cast<int64_t>(by_work) * 16384 < n) by_work <<= 1;
+    while (by_work < 8 && static_cast<int64_t>(by_work) * 8192 < n) by_work <<= 1;
     csize = std::min(csize, by_work);
 
     XchgOut xo = {};

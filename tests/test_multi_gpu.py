@@ -63,6 +63,23 @@ def _rank_main(rank, world, port, tmpdir):
             g.replay()
         torch.cuda.synchronize()
         assert torch.equal(captured, fast)
+        # soak: 200 replays back to back with a different query each time (no host synchronisation between most
+        # of them, so the ranks drift apart as far as the protocol lets them); every checked output must equal
+        # what the NCCL path gives for that query
+        queries = [synth.make_query(k[:, :, sink:sink + n_r], G, seed=50 + i).cuda() for i in range(5)]
+        wants = [step.step(qi).clone() for qi in queries]
+        qbuf = queries[0].clone()
+        g2 = torch.cuda.CUDAGraph()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side), torch.cuda.graph(g2, stream=side):
+            soaked = peer_step.step(qbuf)
+        torch.cuda.current_stream().wait_stream(side)
+        dist.barrier()
+        for it in range(200):
+            qbuf.copy_(queries[it % 5])
+            g2.replay()
+            if it % 16 == 0 or it >= 195:
+                assert torch.equal(soaked, wants[it % 5]), f"replay {it}"
         peer_step.xchg.check()
         eng.check_status()
         torch.cuda.synchronize()

@@ -642,7 +642,7 @@ def run_seq_sharded(cfg, ranks: Ranks, steps, warmup):
                  "ms_per_step_cuda_graph": float(np.median(graph_loops)) if graph_loops else None,
                  "timing": summarise(graph_loops if graph_loops else stream_loops),
                  "collectives_per_step": (2 if world > 1 else 0) if mode == "nccl" else 0,
-                 "kernels_per_step": 6}
+                 "kernels_per_step": 5 if mode == "peer" else 6}
         entry["ms_per_step"] = entry["ms_per_step_cuda_graph"] or entry["ms_per_step_stream_launch"]
         if mode == "peer":
             ranks.barrier()

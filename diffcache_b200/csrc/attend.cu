@@ -430,17 +430,15 @@ sparse_attend_kernel(const AttendArgs a) {
 constexpr int kCombineThreads = 128;
 constexpr int kCombineMaxParts = 1024;
 
+// One row (blockIdx.x) of a merge.  xepoch: epoch the fan-out stores carry (xo.world != 0); want: epoch the polled
+// parts must carry (ll.chan != nullptr).  Uses static shared memory: a kernel that calls it twice separates the
+// calls with a block barrier.
 template <int DT>
-__global__ void __launch_bounds__(kCombineThreads)
-lse_combine_kernel(const float* __restrict__ part_acc, int64_t acc_ps, int64_t acc_rs,
-                   const float* __restrict__ part_ml, int64_t ml_ps, int64_t ml_rs, int n_part, int dim,
-                   uint16_t* __restrict__ out, float* __restrict__ out_lse, float* __restrict__ out_acc,
-                   float* __restrict__ out_ml, const XchgLL ll, int64_t ll_ml_off, const XchgOut xo, int64_t xo_ml_off) {
-    pdl_launch_dependents();
-    pdl_wait();
-    // results that other ranks need go straight into every rank's exchange buffer as well (pair format):
-    // (acc, m, l) of a sequence-sharded step, or the 16-bit output slice of a head-sharded layer
-    const uint32_t xepoch = xo.world ? xchg_next_epoch(xo) : 0u;
+__device__ __forceinline__ void
+combine_row(const float* __restrict__ part_acc, int64_t acc_ps, int64_t acc_rs, const float* __restrict__ part_ml,
+            int64_t ml_ps, int64_t ml_rs, int n_part, int dim, uint16_t* __restrict__ out, float* __restrict__ out_lse,
+            float* __restrict__ out_acc, float* __restrict__ out_ml, const XchgLL& ll, int64_t ll_ml_off, uint32_t want,
+            const XchgOut& xo, int64_t xo_ml_off, uint32_t xepoch) {
     const int64_t row = blockIdx.x;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     __shared__ float s_w[kCombineMaxParts];   // weight of every part: exp2(m_s - M)
@@ -454,7 +452,6 @@ lse_combine_kernel(const float* __restrict__ part_acc, int64_t acc_ps, int64_t a
     __shared__ __align__(16) float s_stage[kXchgMaxWorld * (256 + 4)];
     if (ll.chan != nullptr) {
         const int row_stride = dim + 4;   // dim accumulators, (m, l), padding that keeps rows 16-byte aligned
-        const uint32_t want = ll.epoch[ll.channel];
         const unsigned long long t0 = global_timer_ns();
         bool fail = false;
         const int per = dim / 2 + 1;      // pair vectors per part: dim / 2 of accumulators, one of (m, l)
@@ -580,7 +577,47 @@ lse_combine_kernel(const float* __restrict__ part_acc, int64_t acc_ps, int64_t a
         if (out_ml) { out_ml[row * 2] = M; out_ml[row * 2 + 1] = L; }
         if (xo.world && out_ml) xchg_put2(xo, xepoch, xo.rank_off + xo_ml_off + row * 2, __float_as_uint(M), __float_as_uint(L));
     }
+}
+
+template <int DT>
+__global__ void __launch_bounds__(kCombineThreads)
+lse_combine_kernel(const float* __restrict__ part_acc, int64_t acc_ps, int64_t acc_rs,
+                   const float* __restrict__ part_ml, int64_t ml_ps, int64_t ml_rs, int n_part, int dim,
+                   uint16_t* __restrict__ out, float* __restrict__ out_lse, float* __restrict__ out_acc,
+                   float* __restrict__ out_ml, const XchgLL ll, int64_t ll_ml_off, const XchgOut xo, int64_t xo_ml_off) {
+    pdl_launch_dependents();
+    pdl_wait();
+    // results that other ranks need go straight into every rank's exchange buffer as well (pair format):
+    // (acc, m, l) of a sequence-sharded step, or the 16-bit output slice of a head-sharded layer
+    const uint32_t xepoch = xo.world ? xchg_next_epoch(xo) : 0u;
+    const uint32_t want = ll.chan != nullptr ? ll.epoch[ll.channel] : 0u;
+    combine_row<DT>(part_acc, acc_ps, acc_rs, part_ml, ml_ps, ml_rs, n_part, dim, out, out_lse, out_acc, out_ml, ll,
+                    ll_ml_off, want, xo, xo_ml_off, xepoch);
     if (xo.world) xchg_finish(xo, xepoch, gridDim.x);
+}
+
+// Sequence-sharded step, both sides of the second exchange in one launch: the CTA of a row merges this rank's
+// split partials, stores (acc, m, l) into every rank's copy of the channel, then waits for the other ranks' (acc,
+// m, l) of the same row in its own copy and merges those into the final output.  The second half polls for the
+// epoch the first half has just written with, so it needs no kernel boundary in between; what it waits for is
+// written by the same kernel on the OTHER GPUs, never by a later launch on this one.
+template <int DT>
+__global__ void __launch_bounds__(kCombineThreads)
+lse_combine_exchange_kernel(const float* __restrict__ part_acc, int64_t acc_ps, int64_t acc_rs,
+                            const float* __restrict__ part_ml, int64_t ml_ps, int64_t ml_rs, int n_part, int dim,
+                            float* __restrict__ out_acc, float* __restrict__ out_ml, const XchgOut xo, int64_t ml_off,
+                            const XchgLL ll, uint16_t* __restrict__ out, float* __restrict__ out_lse) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const uint32_t xepoch = xchg_next_epoch(xo);
+    const XchgLL none = {};
+    combine_row<DT>(part_acc, acc_ps, acc_rs, part_ml, ml_ps, ml_rs, n_part, dim, nullptr, nullptr, out_acc, out_ml, none,
+                    0, 0u, xo, ml_off, xepoch);
+    xchg_finish(xo, xepoch, gridDim.x);   // starts with a block barrier: the shared arrays are free again
+    XchgOut off = xo;
+    off.world = 0;
+    combine_row<DT>(nullptr, 0, 0, nullptr, 0, 0, ll.world, dim, out, out_lse, nullptr, nullptr, ll, ml_off, xepoch, off, 0,
+                    0u);
 }
 
 template <int DT, int LPR>
@@ -622,7 +659,9 @@ int64_t attend_scratch_bytes(int n_prob, int group, int head_dim) {
 
 int lse_combine(const float* acc, int64_t acc_ps, int64_t acc_rs, const float* ml, int64_t ml_ps, int64_t ml_rs,
                 int n_part, int64_t rows, int head_dim, int dtype, void* out, float* out_lse, float* out_acc,
-                float* out_ml, cudaStream_t stream, const XchgLL* ll, const XchgOut* xout) {
+                float* out_ml, cudaStream_t stream, const XchgLL* ll, const XchgOut* xout, const XchgFinal* fin) {
+    // fin (may be NULL; needs xout and out_acc / out_ml): after the fan-out the same launch waits for the other
+    // ranks' blocks and writes the merge of all ranks' parts to fin->out
     // ll (may be NULL): the parts arrive in pair format in an exchange channel instead of acc / ml
     // xout (may be NULL): the results are also stored into every rank's copy of an exchange channel, either
     // (out_acc, out_ml) as [acc (rows, dim) | ml (rows, 2)] words or `out` as 16-bit pairs, laid out by xout
@@ -641,6 +680,22 @@ int lse_combine(const float* acc, int64_t acc_ps, int64_t acc_rs, const float* m
     XchgOut xo = {};
     if (xout != nullptr) xo = *xout;
     const int64_t ml_off = rows * head_dim;   // word offset of the (m, l) block inside a part's slot
+    if (fin != nullptr) {
+        DC_REQUIRE(xout != nullptr && out_acc != nullptr && out_ml != nullptr && ll == nullptr && fin->out != nullptr &&
+                       fin->ll.chan != nullptr && fin->ll.world == xo.world && fin->ll.channel == xo.channel,
+                   "lse_combine: the in-kernel final merge needs the fan-out of (acc, m, l) on the same channel");
+        DC_REQUIRE(fin->ll.world <= kXchgMaxWorld && head_dim <= 256 && head_dim % 2 == 0,
+                   "lse_combine: parts from the peer exchange: at most %d parts, even head_dim <= 256", kXchgMaxWorld);
+        if (dtype == DC_BF16)
+            DC_CUDA_TRY(launch_chained(lse_combine_exchange_kernel<DC_BF16>, grid, block, 0, stream, 0u, acc, acc_ps, acc_rs,
+                                       ml, ml_ps, ml_rs, n_part, head_dim, out_acc, out_ml, xo, ml_off, fin->ll,
+                                       static_cast<uint16_t*>(fin->out), fin->out_lse));
+        else
+            DC_CUDA_TRY(launch_chained(lse_combine_exchange_kernel<DC_FP16>, grid, block, 0, stream, 0u, acc, acc_ps, acc_rs,
+                                       ml, ml_ps, ml_rs, n_part, head_dim, out_acc, out_ml, xo, ml_off, fin->ll,
+                                       static_cast<uint16_t*>(fin->out), fin->out_lse));
+        return DC_OK;
+    }
     if (dtype == DC_BF16)
         DC_CUDA_TRY(launch_chained(lse_combine_kernel<DC_BF16>, grid, block, 0, stream, 0u, acc, acc_ps, acc_rs, ml, ml_ps,
                                    ml_rs, n_part, head_dim, static_cast<uint16_t*>(out), out_lse, out_acc, out_ml, w, ml_off,
@@ -658,7 +713,7 @@ int sparse_attend(const void* k_store, const void* v_store, int64_t prob_stride,
                   void* res_v, int64_t res_stride_b, int64_t res_stride_h, int res_len, float scale, void* out,
                   float* out_lse, float* out_acc, float* out_ml, void* scratch, cudaStream_t stream,
                   const int32_t* sel_count, int64_t q_stride_b, int64_t new_stride_b, const int32_t* n_rows_dev,
-                  const int32_t* res_len_dev, const XchgOut* xout) {
+                  const int32_t* res_len_dev, const XchgOut* xout, const XchgFinal* fin) {
     // n_rows_dev / res_len_dev (may be NULL): device words read when the kernel runs, overriding n_rows and
     // res_len, which then only size the launch (res_len = the most resident rows there can be)
     DC_REQUIRE(q != nullptr && scratch != nullptr, "sparse_attend: null q/scratch");
@@ -729,7 +784,7 @@ int sparse_attend(const void* k_store, const void* v_store, int64_t prob_stride,
     if (rc != DC_OK) return rc;
     return lse_combine(a.part_acc, head_dim, static_cast<int64_t>(a.n_split) * head_dim, a.part_ml, 2,
                        static_cast<int64_t>(a.n_split) * 2, a.n_split, static_cast<int64_t>(n_prob) * group, head_dim,
-                       dtype, out, out_lse, out_acc, out_ml, stream, nullptr, xout);
+                       dtype, out, out_lse, out_acc, out_ml, stream, nullptr, xout, fin);
 }
 
 }  // namespace dc
@@ -810,5 +865,5 @@ extern "C" int dc_sparse_attend_noalloc(const void* k_store, const void* v_store
     return sparse_attend(k_store, v_store, prob_stride, n_rows, n_prob, kv_heads, group, head_dim, dtype, q, sel,
                          sel_stride, n_sel, sel_base, k_new, v_new, res_k, res_v, res_stride_b, res_stride_h, res_len,
                          scale, out, out_lse, out_acc, out_ml, scratch, as_stream(stream), nullptr, 0, 0, nullptr, nullptr,
-                         nullptr);
+                         nullptr, nullptr);
 }

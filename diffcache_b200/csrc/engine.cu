@@ -34,13 +34,15 @@ int sparse_attend(const void* k_store, const void* v_store, int64_t prob_stride,
                   void* res_v, int64_t res_stride_b, int64_t res_stride_h, int res_len, float scale, void* out,
                   float* out_lse, float* out_acc, float* out_ml, void* scratch, cudaStream_t stream,
                   const int32_t* sel_count = nullptr, int64_t q_stride_b = 0, int64_t new_stride_b = 0,
-                  const int32_t* n_rows_dev = nullptr, const int32_t* res_len_dev = nullptr, const XchgOut* xout = nullptr);
+                  const int32_t* n_rows_dev = nullptr, const int32_t* res_len_dev = nullptr, const XchgOut* xout = nullptr,
+                  const XchgFinal* fin = nullptr);
 int adaptive_budget(const uint32_t* bits, int64_t stride, int n_prob, int k, int head_dim, const int* seq, int n_seq,
                     float threshold, int32_t* budget, cudaStream_t stream, const int32_t* n_dev = nullptr);
 int64_t attend_scratch_bytes(int n_prob, int group, int head_dim);
 int lse_combine(const float* acc, int64_t acc_ps, int64_t acc_rs, const float* ml, int64_t ml_ps, int64_t ml_rs,
                 int n_part, int64_t rows, int head_dim, int dtype, void* out, float* out_lse, float* out_acc,
-                float* out_ml, cudaStream_t stream, const XchgLL* ll = nullptr, const XchgOut* xout = nullptr);
+                float* out_ml, cudaStream_t stream, const XchgLL* ll = nullptr, const XchgOut* xout = nullptr,
+                const XchgFinal* fin = nullptr);
 int pq_build_lut(const void* q, int q_mode, int group, int dtype, const float* centroids, int n_prob, int head_dim,
                  int n_sub, float* lut, cudaStream_t stream);
 int pq_adc_scan(const uint8_t* codes, int64_t prob_stride, int n_prob, int64_t n, int n_sub, const float* lut,
@@ -924,7 +926,7 @@ static int local_topk_impl(dc_engine* e, const void* q, int topk, uint32_t* out_
 static int attend_owned_impl(dc_engine* e, const void* q, const uint32_t* sel_gidx, int n_sel, const void* k_new,
                             const void* v_new, void* res_k, void* res_v, int64_t res_stride_b, int64_t res_stride_h,
                             int res_len, float scale, float* out_acc, float* out_ml, const int32_t* sel_count,
-                            uint64_t stream, const XchgOut* xout);
+                            uint64_t stream, const XchgOut* xout, const XchgFinal* fin = nullptr);
 
 int dc_attend_owned(dc_engine* e, const void* q, const uint32_t* sel_gidx, int n_sel, const void* k_new,
                     const void* v_new, void* res_k, void* res_v, int64_t res_stride_b, int64_t res_stride_h,
@@ -937,7 +939,7 @@ int dc_attend_owned(dc_engine* e, const void* q, const uint32_t* sel_gidx, int n
 static int attend_owned_impl(dc_engine* e, const void* q, const uint32_t* sel_gidx, int n_sel, const void* k_new,
                             const void* v_new, void* res_k, void* res_v, int64_t res_stride_b, int64_t res_stride_h,
                             int res_len, float scale, float* out_acc, float* out_ml, const int32_t* sel_count,
-                            uint64_t stream, const XchgOut* xout) {
+                            uint64_t stream, const XchgOut* xout, const XchgFinal* fin) {
     DC_ENGINE_ENTER(e);
     DC_REQUIRE(q && out_acc && out_ml, "dc_attend_owned: null pointer");
     int64_t bound = 0;
@@ -946,7 +948,7 @@ static int attend_owned_impl(dc_engine* e, const void* q, const uint32_t* sel_gi
     return sparse_attend(e->k, e->v, e->prob_stride, bound, e->n_prob, e->kv_heads, e->group, e->head_dim,
                          e->dtype, q, sel_gidx, n_sel, n_sel, e->row_offset, k_new, v_new, res_k, res_v, res_stride_b,
                          res_stride_h, res_len, scale, nullptr, nullptr, out_acc, out_ml, e->att_scratch,
-                         as_stream(stream), sel_count, 0, 0, e->len, nullptr, xout);
+                         as_stream(stream), sel_count, 0, 0, e->len, nullptr, xout, fin);
 }
 
 // ---- sequence-sharded step with the two exchanges done by peer stores (exchange.cu) ----
@@ -1029,8 +1031,11 @@ int dc_sharded_local(dc_engine* e, dc_xchg* x, const void* q, int topk, uint64_t
     return trace_mark(e, s);
 }
 
-int dc_sharded_attend(dc_engine* e, dc_xchg* x, const void* q, const void* k_new, const void* v_new, void* res_k,
-                      void* res_v, int64_t res_stride_b, int64_t res_stride_h, int res_len, float scale, uint64_t stream) {
+// fin (may be NULL): the split merge also does the final merge of all ranks' partials (one launch fewer); only for
+// steps whose ranks run on different GPUs, since the kernel then waits for blocks the other ranks' kernels send
+static int sharded_attend_impl(dc_engine* e, dc_xchg* x, const void* q, const void* k_new, const void* v_new, void* res_k,
+                               void* res_v, int64_t res_stride_b, int64_t res_stride_h, int res_len, float scale,
+                               uint64_t stream, const XchgFinal* fin) {
     DC_ENGINE_ENTER(e);
     DC_REQUIRE(x != nullptr && q != nullptr, "dc_sharded_attend: null pointer");
     DC_REQUIRE(e->shard_k > 0, "dc_sharded_attend: dc_sharded_local has not run");
@@ -1046,7 +1051,7 @@ int dc_sharded_attend(dc_engine* e, dc_xchg* x, const void* q, const void* k_new
     xo.row_words = e->head_dim;
     rc = attend_owned_impl(e, q, e->shard_gidx, k, k_new, v_new, res_k, res_v, res_stride_b, res_stride_h, res_len, scale,
                            e->shard_part, e->shard_part + rows * e->head_dim, e->shard_count, stream,
-                           fused_push() ? &xo : nullptr);
+                           fused_push() ? &xo : nullptr, fused_push() ? fin : nullptr);
     if (rc) return rc;
     trace_mark(e, s);
     if (!fused_push()) {
@@ -1054,6 +1059,12 @@ int dc_sharded_attend(dc_engine* e, dc_xchg* x, const void* q, const void* k_new
         if (rc) return rc;
     }
     return trace_mark(e, s);
+}
+
+int dc_sharded_attend(dc_engine* e, dc_xchg* x, const void* q, const void* k_new, const void* v_new, void* res_k,
+                      void* res_v, int64_t res_stride_b, int64_t res_stride_h, int res_len, float scale, uint64_t stream) {
+    return sharded_attend_impl(e, x, q, k_new, v_new, res_k, res_v, res_stride_b, res_stride_h, res_len, scale, stream,
+                               nullptr);
 }
 
 int dc_sharded_combine(dc_engine* e, dc_xchg* x, void* out, float* out_lse, uint64_t stream) {
@@ -1072,6 +1083,16 @@ int dc_sharded_decode_attend(dc_engine* e, dc_xchg* x, const void* q, const void
                              void* out, float* out_lse, uint64_t stream) {
     int rc = dc_sharded_local(e, x, q, topk, stream);
     if (rc) return rc;
+    // All three phases in one call means the ranks run concurrently on their own GPUs, so the split merge may
+    // wait for the other ranks' partials itself and write the final output (DC_XCHG_FUSED=0: separate kernels).
+    if (fused_push() && e != nullptr && x != nullptr && out != nullptr && e->trace_cap == 0) {
+        XchgFinal fin;
+        fin.ll = xchg_ll_args(x, 1);
+        fin.out = out;
+        fin.out_lse = out_lse;
+        return sharded_attend_impl(e, x, q, k_new, v_new, res_k, res_v, res_stride_b, res_stride_h, res_len, scale, stream,
+                                   &fin);
+    }
     rc = dc_sharded_attend(e, x, q, k_new, v_new, res_k, res_v, res_stride_b, res_stride_h, res_len, scale, stream);
     if (rc) return rc;
     return dc_sharded_combine(e, x, out, out_lse, stream);

@@ -45,6 +45,14 @@ struct XchgOut {
     int64_t rows_per_block, block_stride, rank_off, row_words;
 };
 
+// Second half of an exchange done by the producing kernel itself (sequence-sharded step): once its own block is
+// stored to every rank, the kernel waits for the other ranks' blocks in channel `ll` and writes the merged result.
+struct XchgFinal {
+    XchgLL ll;        // this rank's copy of the channel the kernel also fans out to
+    void* out;        // final (rows, head_dim) output in the element type
+    float* out_lse;   // may be NULL
+};
+
 __device__ __forceinline__ int64_t xchg_word_index(const XchgOut& o, int64_t row, int64_t col_word) {
     return (row / o.rows_per_block) * o.block_stride + o.rank_off + (row % o.rows_per_block) * o.row_words + col_word;
 }

@@ -219,7 +219,7 @@ class SequenceShardedStep:
         on all ranks, in ``last_selection``."""
         k = self.topk
         if self.xchg is not None and not want_selection:
-            return self.backend.peer_step(q, k, self.xchg)               # seven kernels, no collective call
+            return self.backend.peer_step(q, k, self.xchg)               # five kernels, no collective call
         bits, gidx = self.backend.local_topk(q, k)                       # (P, k) each, ascending, padded
         P = bits.shape[0]
         use_prefix = self.world * k * 4 <= self.PREFIX_MERGE_MAX_BYTES and hasattr(self.backend, "merge_count")
@@ -289,8 +289,9 @@ class GpuShardBackend:
         return ptr(self.k_new), ptr(self.v_new), ptr(self.res_k), ptr(self.res_v), sb, sh, int(self.res_len)
 
     def peer_step(self, q, k, xchg: PeerExchange):
-        """The whole step as one call: scan, select, key push | prefix count (polls the keys), attention, split
-        merge, partial push | merge (polls the partials).  ``k`` must be even."""
+        """The whole step as one call: scan, select + key fan-out | prefix count (polls the keys), attention, split
+        merge + partial fan-out + final merge (polls the partials).  ``k`` must be even.  Every rank must run on
+        its own GPU: the last kernel waits for what the same kernel of the other ranks sends."""
         out = self._buf("out", (self.e.bsz, self.e.q_head_num, self.D), torch.bfloat16 if self.e.dtype == 0 else torch.float16)
         kn, vn, rk, rv, sb, sh, rl = self._res_args()
         _lib.check(self.lib.dc_sharded_decode_attend(self.e._h, xchg._h, q.data_ptr(), kn, vn, rk, rv, sb, sh, rl, int(k),

@@ -357,9 +357,13 @@ int dc_xchg_check(dc_xchg* x, uint64_t stream);
  *                       resident rows / new token as given there) and pushes the partial result;
  *   dc_sharded_combine  waits for all ranks' partials and merges them by log-sum-exp into `out`
  *                       (bsz, q_heads, head_dim), identical on every rank.
- * dc_sharded_decode_attend runs the three in a row: the whole step is one call and six kernels on
- * `stream` (scan; select, which also stores the keys into every rank's buffer; prefix count; attention;
- * split merge, which also stores the partials into every rank's buffer; final merge; topk must be even), capturable in a CUDA graph once the first call has allocated the per-engine buffers.
+ * dc_sharded_decode_attend is the whole step as one call and five kernels on `stream` (scan; select,
+ * which also stores the keys into every rank's buffer; prefix count; attention; split merge, which
+ * also stores the partials into every rank's buffer and then waits for the other ranks' partials and
+ * writes the final merge; topk must be even), capturable in a CUDA graph once the first call has
+ * allocated the per-engine buffers.  Its last kernel waits for data that the same kernel of the
+ * OTHER ranks sends, so every rank must run on its own GPU; ranks that share a GPU (tests) call
+ * the three phase functions, all ranks' phase n before any rank's phase n + 1.
  * Results are those of dc_decode_attend on the concatenated rows (same ranking keys, ties to the
  * smaller global row id: nsw.rs:74-91,612).
  */

@@ -55,6 +55,7 @@ SIGNATURES = {
     "dc_xchg_collect": (_i32, [_vp, _i32, _vp, _i64, _u64]),
     "dc_xchg_check": (_i32, [_vp, _u64]),
     "dc_set_output_exchange": (_i32, [_vp, _vp, _i32]),
+    "dc_set_output_gather": (_i32, [_vp, _vp]),
     "dc_sharded_slot_bytes": (_i32, [_vp, _i32, _vp]),
     "dc_sharded_local": (_i32, [_vp, _vp, _vp, _i32, _u64]),
     "dc_sharded_attend": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i32, _f32, _u64]),

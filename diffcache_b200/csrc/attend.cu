@@ -636,6 +636,55 @@ int launch_attend(const AttendArgs& a, int n_prob, cudaStream_t stream) {
     return DC_OK;
 }
 
+// Head-sharded layer, both sides of the all-gather in one launch: the CTA of output row (b, h) merges the splits,
+// stores its 16-bit output row into every rank's copy of the channel (xo: rows interleaved by rank, so that the
+// channel reads (bsz, world, q_heads * dim)), then waits in its own copy for row (b, h) of EVERY rank and writes those
+// `world` rows densely to `dense` (bsz, world * q_heads * dim) - what a separate wait-and-unpack kernel did before.
+template <int DT>
+__global__ void __launch_bounds__(kCombineThreads)
+lse_combine_allgather_kernel(const float* __restrict__ part_acc, int64_t acc_ps, int64_t acc_rs,
+                             const float* __restrict__ part_ml, int64_t ml_ps, int64_t ml_rs, int n_part, int dim,
+                             uint16_t* __restrict__ out, float* __restrict__ out_lse, const XchgOut xo, const XchgLL ll,
+                             uint32_t* __restrict__ dense) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const uint32_t xepoch = xchg_next_epoch(xo);
+    const XchgLL none = {};
+    combine_row<DT>(part_acc, acc_ps, acc_rs, part_ml, ml_ps, ml_rs, n_part, dim, out, out_lse, nullptr, nullptr, none, 0,
+                    0u, xo, 0, xepoch);
+    xchg_finish(xo, xepoch, gridDim.x);
+    // words of row (b, h) of rank r: block b, rank offset r * slice, row h of the slice (the layout of xo)
+    const int64_t row = blockIdx.x;
+    const int64_t b = row / xo.rows_per_block, h = row % xo.rows_per_block;
+    const int64_t slice = xo.rows_per_block * xo.row_words;
+    const int vec_per_row = static_cast<int>(xo.row_words / 2);   // 16-byte pair vectors (2 words) per row
+    const unsigned long long t0 = global_timer_ns();
+    bool fail = false;
+    const int total = ll.world * vec_per_row;
+    for (int i0 = threadIdx.x; i0 < total; i0 += 4 * kCombineThreads) {
+        uint4 w[4];
+        const uint4* src[4];
+        int64_t word[4];
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const int i = i0 + j * kCombineThreads;
+            if (i >= total) continue;
+            const int r = i / vec_per_row, v = i % vec_per_row;
+            word[j] = b * xo.block_stride + r * slice + h * xo.row_words + 2 * v;
+            src[j] = ll.chan + word[j] / 2;
+            w[j] = ld_volatile16(src[j]);
+        }
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const int i = i0 + j * kCombineThreads;
+            if (i >= total) continue;
+            uint2 d = make_uint2(w[j].x, w[j].z);
+            if (w[j].y != xepoch || w[j].w != xepoch) d = xchg_poll(src[j], xepoch, ll, t0, fail);
+            *reinterpret_cast<uint2*>(dense + word[j]) = d;
+        }
+    }
+}
+
 }  // namespace
 
 int attend_splits(int n_prob, int total_rows) {
@@ -680,6 +729,20 @@ int lse_combine(const float* acc, int64_t acc_ps, int64_t acc_rs, const float* m
     XchgOut xo = {};
     if (xout != nullptr) xo = *xout;
     const int64_t ml_off = rows * head_dim;   // word offset of the (m, l) block inside a part's slot
+    if (fin != nullptr && out_acc == nullptr) {   // head-sharded layer: fan-out of the 16-bit rows + gather of all ranks' rows
+        DC_REQUIRE(xout != nullptr && out != nullptr && ll == nullptr && fin->out != nullptr && fin->ll.chan != nullptr &&
+                       fin->ll.world == xo.world && fin->ll.channel == xo.channel && xo.row_words % 2 == 0,
+                   "lse_combine: the in-kernel gather needs the fan-out of `out` on the same channel");
+        if (dtype == DC_BF16)
+            DC_CUDA_TRY(launch_chained(lse_combine_allgather_kernel<DC_BF16>, grid, block, 0, stream, 0u, acc, acc_ps, acc_rs,
+                                       ml, ml_ps, ml_rs, n_part, head_dim, static_cast<uint16_t*>(out), out_lse, xo, fin->ll,
+                                       static_cast<uint32_t*>(fin->out)));
+        else
+            DC_CUDA_TRY(launch_chained(lse_combine_allgather_kernel<DC_FP16>, grid, block, 0, stream, 0u, acc, acc_ps, acc_rs,
+                                       ml, ml_ps, ml_rs, n_part, head_dim, static_cast<uint16_t*>(out), out_lse, xo, fin->ll,
+                                       static_cast<uint32_t*>(fin->out)));
+        return DC_OK;
+    }
     if (fin != nullptr) {
         DC_REQUIRE(xout != nullptr && out_acc != nullptr && out_ml != nullptr && ll == nullptr && fin->out != nullptr &&
                        fin->ll.chan != nullptr && fin->ll.world == xo.world && fin->ll.channel == xo.channel,

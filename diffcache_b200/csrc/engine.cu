@@ -254,6 +254,7 @@ struct dc_engine {
     int shard_k = 0;
     dc_xchg* out_xchg = nullptr;      // dc_set_output_exchange: decode steps also fan their output slice out to it
     int out_xchg_channel = 0;
+    void* out_dense = nullptr;         // dc_set_output_gather: where the step's last kernel unpacks all ranks' slices
     int64_t prob_stride = 0;   // elements
     int64_t score_stride = 0;  // elements
     uint16_t* k = nullptr;
@@ -743,6 +744,8 @@ int decode_attend_impl(dc_engine* e, const void* q, int64_t q_stride_b, const vo
     }
     XchgOut xo;
     const XchgOut* xout = nullptr;
+    XchgFinal fin;
+    const XchgFinal* finp = nullptr;
     if (e->out_xchg != nullptr) {   // head-sharded layer: (bsz, q_heads, D) becomes (bsz, world, q_heads * D) on every rank
         xo = xchg_out_args(e->out_xchg, e->out_xchg_channel);
         const int64_t slice_words = static_cast<int64_t>(e->q_heads) * e->head_dim / 2;
@@ -751,11 +754,17 @@ int decode_attend_impl(dc_engine* e, const void* q, int64_t q_stride_b, const vo
         xo.rank_off = xchg_rank(e->out_xchg) * slice_words;
         xo.row_words = e->head_dim / 2;
         xout = &xo;
+        if (e->out_dense != nullptr) {   // the merge kernel also waits for all ranks' slices and unpacks them
+            fin.ll = xchg_ll_args(e->out_xchg, e->out_xchg_channel);
+            fin.out = e->out_dense;
+            fin.out_lse = nullptr;
+            finp = &fin;
+        }
     }
     rc = sparse_attend(e->k, e->v, e->prob_stride, bound, e->n_prob, e->kv_heads, e->group, e->head_dim, e->dtype,
                        q, e->sel_idx, k, k, 0, k_new, v_new, res_k, res_v, res_stride_b, res_stride_h, res_len, scale,
                        out, out_lse, nullptr, nullptr, e->att_scratch, s, sel_count, q_stride_b, new_stride_b, e->len,
-                       res_len_dev, xout);
+                       res_len_dev, xout, finp);
     if (rc) return rc;
     if (ev) {
         DC_CUDA_TRY(cudaEventRecord(ev[3], s));
@@ -975,6 +984,16 @@ int dc_set_output_exchange(dc_engine* e, dc_xchg* x, int channel) {
     }
     e->out_xchg = x;
     e->out_xchg_channel = channel;
+    if (x == nullptr) e->out_dense = nullptr;
+    return DC_OK;
+}
+
+int dc_set_output_gather(dc_engine* e, void* dense) {
+    DC_ENGINE_ENTER(e);
+    DC_REQUIRE(dense == nullptr || e->out_xchg != nullptr, "dc_set_output_gather: dc_set_output_exchange comes first");
+    DC_REQUIRE(dense == nullptr || (is_device_ptr(dense) && (reinterpret_cast<uintptr_t>(dense) & 15) == 0),
+               "dc_set_output_gather: a 16-byte aligned device pointer is needed");
+    e->out_dense = dense;
     return DC_OK;
 }
 

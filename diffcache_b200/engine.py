@@ -300,6 +300,14 @@ class DiffCacheGPU:
         switches it off), interleaved so that the channel reads ``(bsz, world, q_head_num * head_dim)``."""
         _lib.check(self._lib.dc_set_output_exchange(self._h, None if exchange is None else exchange._h, int(channel)))
 
+    def set_output_gather(self, dense) -> None:
+        """After :meth:`set_output_exchange`: the kernel that stores the slice also waits for every rank's slice
+        and writes all of them to ``dense`` ``(bsz, world * q_head_num * head_dim)`` (a device tensor that must
+        stay alive; ``None`` switches it off), so no separate ``PeerExchange.collect`` is needed.  Ranks must
+        run on different GPUs."""
+        _lib.check(self._lib.dc_set_output_gather(self._h, _ptr(dense)))
+        self._out_dense = dense
+
     def window_push(self, k_new, v_new, res_k, res_v, window_state, stream=None) -> None:
         """Append the step's new token to this layer's window ring (see ``dc_window_push``): the oldest
         token is spilled into the scanned store once the window is full.  ``window_state`` is the int32

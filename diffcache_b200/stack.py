@@ -19,6 +19,7 @@ the exchange so that a fast rank never overwrites a block a slow rank is still r
 """
 from __future__ import annotations
 
+import os
 from typing import Optional
 
 import torch
@@ -102,6 +103,8 @@ class AttentionStack:
                     if exchange == "peer":
                         raise
         self.exchange = "peer" if self.xchg is not None else ("nccl" if self.world > 1 else "none")
+        # DC_STACK_FUSED_GATHER=0: the all-gather's consumer side stays a kernel of its own (PeerExchange.collect)
+        self.fused_gather = os.environ.get("DC_STACK_FUSED_GATHER", "1") != "0"
         self._last_channel = -1
         torch.cuda.synchronize(self.device)
 
@@ -129,14 +132,18 @@ class AttentionStack:
             self._last_channel = ch
             self.engines[layer].set_output_exchange(self.xchg if self.xchg is not None else None, max(ch, 0))
             # with the peer exchange the step's last kernel also stores the slice into every rank's buffer,
-            # where it lands as (B, world, q_local*D)
+            # where it lands as (B, world, q_local*D), waits there for the other ranks' slices and unpacks all
+            # of them into the dense buffer the projection reads
+            if self.xchg is not None and self.fused_gather:
+                self.engines[layer].set_output_gather(self.xchg_views[ch])
             self.engines[layer].decode_attend(q, self.attn_local, self.topk, res_k=self.res_k[layer],
                                               res_v=self.res_v[layer], res_len=self.res_rows, k_new=kn, v_new=vn)
             if probe is not None and layer == 0:
                 probe.update(q=q.clone(), k_new=kn.clone(), v_new=vn.clone(), attn=self.attn_local.clone())
             if self.xchg is not None:
                 attn = self.xchg_views[ch]
-                self.xchg.collect(ch, attn)                           # waits for all slices, unpacks them densely
+                if not self.fused_gather:
+                    self.xchg.collect(ch, attn)                       # waits for all slices, unpacks them densely
             elif self.world > 1:
                 dist.all_gather_into_tensor(self.attn_full.view(-1), self.attn_local.view(-1), group=self.pg)
                 attn = self.attn_full.view(self.world, B, self.kv_local, -1).permute(1, 0, 2, 3).reshape(B, -1)

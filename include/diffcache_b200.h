@@ -378,6 +378,15 @@ int dc_sharded_slot_bytes(dc_engine* e, int topk, int64_t* out2);
  * round-robin) unless something else orders the ranks between them.
  */
 int dc_set_output_exchange(dc_engine* e, dc_xchg* x, int channel);
+/*
+ * With dc_set_output_gather(e, dense) the kernel that stores the slice also does the consumer's side: it then
+ * waits, in this rank's copy of the channel, for the same output rows of every rank and writes all slices
+ * densely to `dense` ((bsz, world * q_heads * head_dim) elements, device memory) - the all-gather is complete
+ * when the decode call's kernels are, without dc_xchg_collect.  Every rank must run on its own GPU (the kernel
+ * waits for what the same kernel of the other ranks sends).  dense = NULL switches it off;
+ * dc_set_output_exchange(e, NULL, ..) does too.
+ */
+int dc_set_output_gather(dc_engine* e, void* dense);
 int dc_sharded_local(dc_engine* e, dc_xchg* x, const void* q, int topk, uint64_t stream);
 int dc_sharded_attend(dc_engine* e, dc_xchg* x, const void* q, const void* k_new, const void* v_new, void* res_k,
                       void* res_v, int64_t res_stride_b, int64_t res_stride_h, int res_len, float scale, uint64_t stream);

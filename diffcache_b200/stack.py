@@ -12,10 +12,11 @@ With ``world > 1`` the stack is sharded by KV head: rank r owns kv heads
 rows of the fused projection, so scan / select / attend are local; the per-layer exchange is one
 all-gather of the attention output slice ``(B, Hq/world * D)`` before a replicated output
 projection (deterministic: every rank computes the same residual stream).  That all-gather is
-either an NCCL call or (``exchange="peer"``) a push of the slice into every rank's buffer with
-stores over NVLink, interleaved so that the buffer reads ``(B, Hq*D)``, plus a small kernel that waits
-for all slices and unpacks them (:class:`diffcache_b200.sharded.PeerExchange`); consecutive layers use different channels of
-the exchange so that a fast rank never overwrites a block a slow rank is still reading.
+either an NCCL call or (``exchange="peer"``) done by the attention's own merge kernel: it stores the slice into
+every rank's buffer over NVLink, interleaved so that the buffer reads ``(B, Hq*D)``, then waits for the other
+ranks' slices and unpacks all of them for the projection (:class:`diffcache_b200.sharded.PeerExchange`,
+``DiffCacheGPU.set_output_gather``); consecutive layers use different channels of the exchange so that a fast
+rank never overwrites a block a slow rank is still reading.
 """
 from __future__ import annotations
 

@@ -1104,7 +1104,11 @@ int dc_sharded_decode_attend(dc_engine* e, dc_xchg* x, const void* q, const void
     if (rc) return rc;
     // All three phases in one call means the ranks run concurrently on their own GPUs, so the split merge may
     // wait for the other ranks' partials itself and write the final output (DC_XCHG_FUSED=0: separate kernels).
-    if (fused_push() && e != nullptr && x != nullptr && out != nullptr && e->trace_cap == 0) {
+    static const bool fuse_final = [] {   // DC_XCHG_FUSED_FINAL=0: the final merge stays a kernel of its own
+        const char* v = std::getenv("DC_XCHG_FUSED_FINAL");
+        return !(v != nullptr && v[0] == '0');
+    }();
+    if (fuse_final && fused_push() && e != nullptr && x != nullptr && out != nullptr && e->trace_cap == 0) {
         XchgFinal fin;
         fin.ll = xchg_ll_args(x, 1);
         fin.out = out;

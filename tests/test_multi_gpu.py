@@ -124,13 +124,18 @@ def _stack_rank_main(rank, world, port, tmpdir):
         for e in sharded_stack.engines:
             e.check_status()
         torch.cuda.synchronize()
-        peer_stack = AttentionStack(exchange="peer", **kw)         # the all-gather done by peer stores instead
-        assert peer_stack.exchange == "peer"
-        for _ in range(2):
-            assert torch.equal(peer_stack.step(x), y)
-        peer_stack.xchg.check()
-        dist.barrier()
-        peer_stack.close()
+        # the all-gather done by peer stores instead: both sides inside the attention's merge kernel (default), and
+        # with the consumer side left to the separate wait-and-unpack kernel
+        for fused in ("1", "0"):
+            os.environ["DC_STACK_FUSED_GATHER"] = fused
+            peer_stack = AttentionStack(exchange="peer", **kw)
+            assert peer_stack.exchange == "peer" and peer_stack.fused_gather == (fused == "1")
+            for _ in range(3):
+                assert torch.equal(peer_stack.step(x), y)
+            peer_stack.xchg.check()
+            dist.barrier()
+            peer_stack.close()
+        os.environ.pop("DC_STACK_FUSED_GATHER", None)
         if rank == 0:  # the same stack on one GPU: world of one
             solo = AttentionStack(unsharded=True, **kw)
             want = solo.step(x)

@@ -288,6 +288,23 @@ def test_engine_query_matches_reference_semantics(oracle_lib, dtype):
     eng2.close()
 
 
+def test_get_keys_in_several_chunks(oracle_lib):
+    """get_keys to a host array converts a bounded number of problems at a time (at most 64 MB of fp32 on the
+    device): 8 problems x 20 000 rows x 128 x 4 bytes = 82 MB go through in two chunks."""
+    from diffcache_b200 import DiffCacheGPU
+
+    B, Hkv, n, D = 2, 4, 20000, 128
+    g = torch.Generator().manual_seed(31)
+    k = torch.randn((B, Hkv, n, D), generator=g).to(torch.bfloat16)
+    ku = k.view(torch.int16).numpy().view(np.uint16)
+    eng = DiffCacheGPU(B, Hkv, Hkv, D, max_ctx_len=n + 5)   # store rows longer than the filled part
+    eng.prefill(ku.copy(), ku.copy(), None)
+    got = eng.get_keys()
+    assert got.shape == (B, Hkv, n, D)
+    assert np.array_equal(got, oracle_lib.to_f32(ku, 0))
+    eng.close()
+
+
 def test_engine_insert_appends_rows(oracle_lib):
     from diffcache_b200 import DiffCacheError, DiffCacheGPU
 

@@ -63,6 +63,25 @@ def test_scan_matches_oracle(lib, oracle_lib, dtype, D):
             assert mm[p, 0] == got[p].min() and mm[p, 1] == got[p].max()
 
 
+def test_scan_few_wave_launch(lib, oracle_lib):
+    """8 problems x 131 072 rows (one rank's share of the 1M-token sequence on 8 GPUs): the scan takes a chunk size
+    that fills whole waves (1792 rows, the last chunk of a problem is ragged); every key against the oracle."""
+    P, n, D = 8, 131072, 128
+    g = torch.Generator(device="cuda").manual_seed(77)
+    keys = torch.randn((P, n, D), generator=g, device="cuda").to(torch.bfloat16)
+    qm = torch.randn((P, D), generator=g, device="cuda").to(torch.bfloat16)
+    ku = keys.view(torch.int16).cpu().numpy().view(np.uint16)
+    qu = qm.view(torch.int16).cpu().numpy().view(np.uint16)
+    got, mm = _scan(lib, keys.view(torch.int16), qm.view(torch.int16), n, D, 0, 0, 1)
+    for p in (0, 3, 7):
+        want = oracle_lib.score_rows(ku[p], qu[p], 0)
+        gd = got[p].view(np.float32).astype(np.float64)
+        wd = want.view(np.float32).astype(np.float64)
+        assert np.all(np.abs(gd - wd) <= util.ulp_of_dist(want)), "dist differs by more than one ulp"
+        assert np.mean(got[p] == want) >= 0.9
+        assert mm[p, 0] == got[p].min() and mm[p, 1] == got[p].max()
+
+
 @pytest.mark.parametrize("dtype", ["bf16", "fp16"])
 @pytest.mark.parametrize("D", [64, 128, 256])
 def test_scan_variants_agree(lib, monkeypatch, dtype, D):
